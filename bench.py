@@ -1,0 +1,295 @@
+#!/usr/bin/env python
+"""Benchmark of the contraction hot path: descriptor -> plan -> prepare -> timed launches.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5|cfg1] [--impl reference]
+
+A step is one contraction launch.  With N > 1 (started by torch.distributed.run, one rank per
+GPU) the contraction is cut along an external output mode: every rank owns a slice, no
+collective is on the data path, and the global problem grows with N (weak scaling).  Rank 0
+prints one JSON line.
+
+`--impl reference` times the reference's own CPU contraction (its OpenMP verification loop,
+compiled from its sources into oracle/_ref; the repository's CPU restatement when that file is
+absent) on the host cores, on a bounded slab of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# workload -> (modeC, modeA, modeB, extents, scalar, seed, lo, hi, shard mode, roofline bound, cpu-sample mode, cpu-sample extent)
+WORKLOADS = {
+    "cfg1": ("abcd", "aebf", "fdec", dict(a=24, b=24, c=24, d=24, e=16, f=16), 1, 0, -1.0, 1.0, "d", "tensor", "d", 24),
+    "cfg2": ("abc", "adc", "db", dict(a=256, c=256, b=1024, d=1024), 0, 1, -1.0, 1.0, "c", "tensor", "c", 32),
+    "cfg3": ("abcijk", "aeij", "bcek", dict(a=48, b=48, c=48, e=48, i=24, j=24, k=24), 1, 2, -0.5, 0.5, "k", "hbm", "k", 1),
+    "cfg4": ("abcde", "efba", "cfd", dict(a=48, b=48, c=48, d=48, e=48, f=8), 0, 3, -1.0, 1.0, "d", "hbm", "d", 24),
+    "cfg5": ("abcd", "aebf", "cfde", dict(a=128, b=128, c=128, d=128, e=128, f=128), 0, 4, -1.0, 1.0, "d", "tensor", "d", 1),
+}
+REF_CASE = {"cfg1": 21, "cfg2": 18}   # reference loop nests with the same mode pattern (tccg_verify.cpp:660-689, :567-592)
+
+
+def describe(name):
+    mC, mA, mB, ext, st, *_ = WORKLOADS[name]
+    e = ",".join(f"{k}={v}" for k, v in sorted(ext.items()))
+    return f"{name}: C[{','.join(mC)}]=sum A[{','.join(mA)}]*B[{','.join(mB)}] {e} {'FP64' if st else 'TF32'} column-major"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples taken while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc, self.path = None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self, gpu_indices):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.proc.wait()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9 or not f[0].isdigit() or int(f[0]) not in gpu_indices:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.path)
+        # samples under load only: the upper half of what was seen
+        sm.sort()
+        busy = sm[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline(name: str, max_seconds: float = 60.0):
+    """The reference's CPU contraction on a slab of the workload. Returns (dict, tflops)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle_lib import Contraction, Oracle, RefVerifier
+    mC, mA, mB, ext, st, seed, lo, hi, _, _, smode, sext = WORKLOADS[name]
+    ext = dict(ext)
+    full = ext[smode]
+    ext[smode] = min(sext, full)
+    c = Contraction(mC, mA, mB, ext, st)
+    oracle = Oracle()
+    A, B = oracle.inputs(c, seed, lo, hi)
+    sample = f"{name} with {smode}={ext[smode]} of {full} (a {ext[smode]}/{full} slab of the outputs, all other modes full)"
+    use_ref = RefVerifier.available() and name in REF_CASE
+    if use_ref:
+        ref = RefVerifier()
+        out = np.zeros(c.size(c.modeC), dtype=c.dtype)
+        sys.stdout.flush()
+        saved = os.dup(1)
+        devnull = os.open(os.devnull, os.O_WRONLY)
+        os.dup2(devnull, 1)                      # the reference prints its comparison report to stdout
+        try:
+            t0 = time.perf_counter()
+            ref.verify(REF_CASE[name], c, out, A, B)
+            dt = time.perf_counter() - t0
+        finally:
+            os.dup2(saved, 1)
+            os.close(devnull)
+            os.close(saved)
+        kind = "reference"
+        sample += "; timed through the reference's verify_tccg_case, comparator pass included"
+    else:
+        t0 = time.perf_counter()
+        oracle.contract(c, A, B)
+        dt = time.perf_counter() - t0
+        kind = "port"
+    tflops = c.flops() / dt / 1e12
+    return {"value": tflops, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": kind, "sample": sample,
+            "seconds": dt}, tflops
+
+
+def run_reference(args, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    info = None
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_baseline(name)
+    for _ in range(max(1, min(args.steps, 3))):
+        info, v = cpu_baseline(name)
+        vals.append(v)
+    v = statistics.mean(vals)
+    info["value"] = v
+    mC, mA, mB, ext, st, *_ = WORKLOADS[name]
+    line = {"impl": "reference", "metric": "contraction throughput", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": len(vals), "warmup": 1, "ms_per_step": info["seconds"] * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f64",
+            "data": "synthetic", "config": {"workload": describe(name)}, "cpu_baseline": info,
+            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--backend", default="model", choices=["model", "cogent", "ttgt"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    args = ap.parse_args()
+    name = args.workload
+    if args.impl == "reference":
+        run_reference(args, name)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import tcont_b200 as tc
+    from tcont_b200 import api, sharding
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path (use --impl reference for the CPU baseline)")
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    mC, mA, mB, ext, st, seed, lo, hi, shard_mode, bound, _, _ = WORKLOADS[name]
+    sel = {"model": 0, "cogent": 1, "ttgt": 2}[args.backend]
+    local_eq = tc.TCEquation(mC, mA, mB, dict(ext), "-", tc.ScalarType(st), tc.BackendSelection(sel))
+    global_eq = sharding.grow_equation(local_eq, shard_mode, world)
+    # every rank generates its own slice of the global inputs: the sharded operand at the
+    # rank's offset of the stream, the shared operand identically everywhere
+    nA, nB = local_eq.size(mA), local_eq.size(mB)
+    a_sharded = shard_mode in mA
+    A = tc.fill_uniform(nA, local_eq.scalar_type, seed, rank * nA if a_sharded else 0, lo, hi)
+    offB = world * nA if a_sharded else nA
+    B = tc.fill_uniform(nB, local_eq.scalar_type, seed, offB + (0 if a_sharded else rank * nB), lo, hi)
+    plan = tc.plan(local_eq)
+    run = tc.prepare(plan, A, B)
+    desc = plan.describe()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    tc.warmup(run, max(args.warmup, 3))
+    sampler = ClockSampler()
+    if rank == 0:
+        sampler.start()
+    sync_all()
+    ms, launches = run.time_launches(args.steps)
+    sync_all()
+    clocks = sampler.stop(set(range(world))) if rank == 0 else None
+    if run.device_status() != 0:
+        raise SystemExit("a kernel reported a timed-out wait; the numbers are invalid")
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    flops_local = plan.flops
+    value = world * flops_local / (ms_step * 1e-3) / 1e12
+
+    # end to end through the host-buffer entry point: pinned host A, B -> device, launch, C -> pinned host
+    hA = torch.from_numpy(A).pin_memory()
+    hB = torch.from_numpy(B).pin_memory()
+    hC = torch.empty(local_eq.size(mC), dtype=hA.dtype).pin_memory()
+    run.contract_host_ptr(hA.data_ptr(), hB.data_ptr(), hC.data_ptr())
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    h2d = d2h = 0
+    for _ in range(args.e2e_steps):
+        h2d, d2h = run.contract_host_ptr(hA.data_ptr(), hB.data_ptr(), hC.data_ptr())
+    e1.record()
+    torch.cuda.synchronize()
+    te = torch.tensor([e0.elapsed_time(e1) / args.e2e_steps], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item())
+    e2e_value = world * flops_local / (e2e_ms * 1e-3) / 1e12
+    checksum = float(hC[:: max(1, hC.numel() // 4096)].double().abs().sum())
+
+    if rank == 0:
+        peaks = measured_peaks()
+        elt = 8 if st else 4
+        alg_bytes = (nA + nB + local_eq.size(mC)) * elt
+        if bound == "tensor":
+            # TF32 dense rate is half the bf16 rate of the same tensor cores; FP64 has no measured
+            # entry in the peaks file, so an FP64 tensor-bound workload reports against HBM instead.
+            peak = peaks["bf16_tflops"] / 2.0 if st == 0 else None
+            achieved = flops_local / (ms_step * 1e-3) / 1e12
+            unit = "TFLOP/s"
+        if bound == "hbm" or peak is None:
+            bound_used, peak, unit = "hbm", peaks["hbm_gbs"], "GB/s"
+            achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+        else:
+            bound_used = "tensor"
+        roofline = {"bound": bound_used, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                    "traffic": None, "kernel": desc["kernel"], "peak_source": peaks["source"] +
+                    (" bf16 dense / 2 (TF32 rate)" if bound_used == "tensor" else " copy bandwidth"),
+                    "algorithmic_bytes_per_launch": alg_bytes, "flops_per_launch": flops_local}
+        line = {"metric": "contraction throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f64" if st else "tf32", "data": "synthetic",
+                "config": {"workload": describe(name), "global": {shard_mode: int(global_eq.extent[shard_mode])},
+                           "sharded_mode": shard_mode, "backend": desc["backend"], "kernel": desc["kernel"],
+                           "l2": "inputs and output exceed the 126 MB L2" if alg_bytes > 126e6 else "working set fits L2",
+                           "timing": "CUDA events on the launching stream, max over ranks"},
+                "clocks": clocks, "gpu_launches": int(launches),
+                "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                        "ms_per_step": e2e_ms, "checksum": checksum},
+                "roofline": roofline}
+        if world == 1 and not args.no_cpu_baseline:
+            info, _ = cpu_baseline(name)
+            line["cpu_baseline"] = info
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

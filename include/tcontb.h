@@ -1,0 +1,147 @@
+/*
+ * tcontb.h -- C ABI of the B200 tensor-contraction engine (libtcontb.so).
+ *
+ * One binary contraction  C[modeC] = sum_K A[modeA] * B[modeB]  on column-major tensors (first
+ * mode fastest), FP64 or "Float32 = TF32 multiply, FP32 accumulate", executed by hand-written
+ * sm_100a kernels.  The semantics are the reference's effective ones: alpha = 1, beta = 0, the
+ * descriptor's sign character is carried but ignored, so every launch overwrites C
+ * (reference: backends/ttgt_cutt/src/ttgt_cutt.cpp:742-743, benchmarks/tccg/tccg_verify.cpp:35-37).
+ *
+ * Each entry point names the piece of the reference's C++ surface (include/tcont.hpp,
+ * src/tcont.cpp) it stands behind; include/tcont.hpp of this repository re-creates that C++
+ * surface on top of these functions.  There is no CPU fallback: every compute entry point fails
+ * with TCONTB_RUNTIME_ERROR when no CUDA device is usable.
+ *
+ * Threading: plans and runs are independent objects; a run must be used by one thread at a
+ * time.  All device work of a run is issued to the run's stream, by default the legacy NULL
+ * stream of the device that was current at tcontb_run_create (the reference launches
+ * everything on the NULL stream, benchmarks/tccg/bench_tccg.cpp:132-136).
+ */
+#ifndef TCONTB_H
+#define TCONTB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    TCONTB_OK = 0,
+    TCONTB_INVALID_ARGUMENT = 1, /* maps to std::invalid_argument in the C++ surface */
+    TCONTB_RUNTIME_ERROR = 2,    /* maps to std::runtime_error (CUDA failures, no device) */
+    TCONTB_UNSUPPORTED = 3       /* a descriptor the engine cannot express (batch modes ...) */
+} tcontb_status;
+
+enum { TCONTB_F32 = 0, TCONTB_F64 = 1 };                 /* TconT::ScalarType, tcont.hpp:12-15 */
+enum { TCONTB_SELECT_MODEL = 0, TCONTB_SELECT_DIRECT = 1, TCONTB_SELECT_TTGT = 2 }; /* BackendSelection, tcont.hpp:44-48 */
+enum { TCONTB_BACKEND_DIRECT = 0, TCONTB_BACKEND_TTGT = 1 };  /* Backend {COGENT, TTGT_CUTT}, tcont.hpp:39-42 */
+
+/* Plain-C image of TconT::TCEquation (tcont.hpp:74-83). Mode names are single characters;
+ * ext_mode[i] has extent ext_val[i]. */
+typedef struct tcontb_desc {
+    int nC, nA, nB;
+    const char* modeC;
+    const char* modeA;
+    const char* modeB;
+    char op;              /* '+', '-', ... : carried, ignored (see above) */
+    int scalar_type;      /* TCONTB_F32 | TCONTB_F64 */
+    int n_ext;
+    const char* ext_mode;
+    const int64_t* ext_val;
+    int backend_selection; /* TCONTB_SELECT_* */
+} tcontb_desc;
+
+typedef struct tcontb_plan tcontb_plan; /* behind TconT::ExecutionPlan / PlanImpl, tcont.hpp:105-131 */
+typedef struct tcontb_run tcontb_run;   /* behind TconT::ExecutionRun / RunImpl, tcont.hpp:111-135 */
+
+/* Last error text of the calling thread ("" when none). */
+const char* tcontb_last_error(void);
+
+/* ---- planning (host only, needs no GPU) ------------------------------------------------- */
+
+/* TconT::plan (src/tcont.cpp:58-88): validates the descriptor, classifies modes into the
+ * GEMM-like M/N/K groups, fuses adjacent modes, picks backend, kernel family and tile shape.
+ * Replaces the reference's LightGBM selector, Python planner and NVRTC step; nothing is
+ * compiled at run time. */
+tcontb_status tcontb_plan_create(const tcontb_desc* desc, tcontb_plan** out);
+void tcontb_plan_destroy(tcontb_plan* plan);
+/* ExecutionPlan::backend (tcont.hpp:126): TCONTB_BACKEND_DIRECT prints as "cogent",
+ * TCONTB_BACKEND_TTGT as "ttgt". */
+int tcontb_plan_backend(const tcontb_plan* plan);
+/* Planner decisions as one JSON object (groups, fusion, kernel, tiles); for tests and logs. */
+tcontb_status tcontb_plan_describe(const tcontb_plan* plan, char* buf, size_t buf_bytes);
+/* 2*sqrt(|A||B||C|), the reference's operation count (src/tcont.cpp:51-55). */
+double tcontb_plan_flops(const tcontb_plan* plan);
+
+/* ---- runs (device) ---------------------------------------------------------------------- */
+
+/* TconT::prepare (src/tcont.cpp:90-100): allocates A, B, C (and transpose scratch) on the
+ * current device, generates host inputs and uploads them.  The reference fills inputs with
+ * rand() in [0,1] seeded by time (backends/cogent/src/cogent.cpp:284-288); here the stream is
+ * tcontb_fill_uniform with seed TCONT_SEED (default: time based) and range TCONT_INPUT_RANGE
+ * "lo:hi" (default 0:1). */
+tcontb_status tcontb_run_create(const tcontb_plan* plan, tcontb_run** out);
+/* Same, but with caller-provided host inputs (|A| and |B| elements of the scalar type), which
+ * the run copies and keeps. */
+tcontb_status tcontb_run_create_with_inputs(const tcontb_plan* plan, const void* a_host, const void* b_host,
+                                            tcontb_run** out);
+/* Same, but on caller-owned DEVICE buffers (no host copies are kept, tcontb_run_host_input
+ * returns NULL): the form a caller uses whose tensors already live in HBM. */
+tcontb_status tcontb_run_create_on_device(const tcontb_plan* plan, const void* a_dev, const void* b_dev, void* c_dev,
+                                          tcontb_run** out);
+void tcontb_run_destroy(tcontb_run* run);
+
+/* Stream all later work of the run is issued to (a cudaStream_t; NULL = legacy NULL stream). */
+tcontb_status tcontb_run_set_stream(tcontb_run* run, void* cuda_stream);
+/* Replaces the run's inputs by an asynchronous host-to-device copy on the run's stream. */
+tcontb_status tcontb_run_upload_inputs(tcontb_run* run, const void* a_host, const void* b_host);
+
+/* TconT::launch (src/tcont.cpp:102-108): one contraction, asynchronous. */
+tcontb_status tcontb_run_launch(tcontb_run* run);
+/* TconT::warmup (src/tcont.cpp:110-124): `iterations` launches, then a device synchronize. */
+tcontb_status tcontb_run_warmup(tcontb_run* run, int iterations);
+/* TconT::zero_output (src/tcont.cpp:126-132): memset of C on the run's stream. */
+tcontb_status tcontb_run_zero_output(tcontb_run* run);
+/* TconT::stage_times (tcont.hpp:96-103): out = {available, total, transpose_a, transpose_b,
+ * contraction, transpose_c} in ms for the most recent launch; measured only when the
+ * environment has TCONT_STAGE_TIMES=1 (otherwise available = 0). */
+tcontb_status tcontb_run_stage_times(tcontb_run* run, float out[6]);
+/* TconT::input_left_host_data / input_right_host_data (tcont.hpp:144-145): which = 0 (A), 1 (B). */
+const void* tcontb_run_host_input(const tcontb_run* run, int which);
+/* TconT::copy_output_to_host (src/tcont.cpp:158-167): blocking device-to-host copy of C. */
+tcontb_status tcontb_run_copy_output(tcontb_run* run, void* dst, size_t bytes);
+
+/* `iterations` launches bracketed by CUDA events on the run's stream; returns the elapsed
+ * milliseconds (the reference harness's timing loop, benchmarks/tccg/bench_tccg.cpp:125-138).
+ * If kernel_launches is not NULL it receives the number of kernels the engine launched. */
+tcontb_status tcontb_run_time_launches(tcontb_run* run, int iterations, float* elapsed_ms, int64_t* kernel_launches);
+/* One pass through the caller-facing path with HOST buffers: upload A and B, launch, download
+ * C, synchronize.  Bytes moved are reported. */
+tcontb_status tcontb_run_contract_host(tcontb_run* run, const void* a_host, const void* b_host, void* c_host,
+                                       int64_t* h2d_bytes, int64_t* d2h_bytes);
+
+/* Device status word of the most recent launch: 0, or a non-zero code when a bounded wait
+ * inside a kernel gave up (the kernel then returns instead of hanging). */
+tcontb_status tcontb_run_device_status(tcontb_run* run, int* status);
+
+/* ---- utilities ---------------------------------------------------------------------------- */
+
+/* Counter-based uniform fill (host): element i = lo + (hi-lo)*u_i, u_i = top 53 bits of
+ * splitmix64(seed*0x9E3779B97F4A7C15 + offset + i) * 2^-53, rounded to float for TCONTB_F32.
+ * A uses offset 0, B uses offset |A|.  Stands in for the reference's rand() fill
+ * (backends/cogent/helper/tcl_helper.h:14-29) so that tests can regenerate identical inputs. */
+tcontb_status tcontb_fill_uniform(void* dst, int scalar_type, int64_t n, uint64_t seed, uint64_t offset, double lo,
+                                  double hi);
+
+/* Stand-alone tensor permutation on the device (the engine's replacement for the cuTT calls of
+ * backends/ttgt_cutt/src/ttgt_cutt.cpp:732-760): dst mode i = src mode perm[i]; column-major;
+ * elem_bytes 4 or 8; pointers are device pointers; asynchronous on `cuda_stream`. */
+tcontb_status tcontb_transpose(const void* src_dev, void* dst_dev, int rank, const int64_t* src_extent, const int* perm,
+                               int elem_bytes, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TCONTB_H */

@@ -1,0 +1,529 @@
+// api.cpp -- the C ABI of include/tcontb.h: plan and run objects around the sm_100a kernels.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <ctime>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/tcontb.h"
+#include "kernels.hpp"
+#include "planner.hpp"
+
+using namespace tcontb;
+
+struct tcontb_plan {
+    Plan plan;
+};
+
+namespace {
+
+thread_local std::string g_last_error;
+
+tcontb_status fail(tcontb_status st, const std::string& msg)
+{
+    g_last_error = msg;
+    return st;
+}
+
+#define TC_CUDA(expr)                                                                                     \
+    do {                                                                                                  \
+        const cudaError_t e_ = (expr);                                                                    \
+        if (e_ != cudaSuccess)                                                                            \
+            return fail(TCONTB_RUNTIME_ERROR, std::string("CUDA error in " #expr ": ") + cudaGetErrorString(e_)); \
+    } while (0)
+
+inline uint64_t splitmix64(uint64_t z)
+{
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+struct DeviceBuffer {
+    void* ptr = nullptr;
+    ~DeviceBuffer()
+    {
+        if (ptr) cudaFree(ptr);
+    }
+    cudaError_t alloc(size_t bytes) { return cudaMalloc(&ptr, bytes ? bytes : 1); }
+};
+
+}  // namespace
+
+struct tcontb_run {
+    Plan plan;
+    int device = 0;
+    int num_sms = 148;
+    cudaStream_t stream = nullptr;
+    size_t elt = 8;
+    // caller-facing buffers: L (left), R (right), C
+    DeviceBuffer ownL, ownR, ownC;
+    void *dL = nullptr, *dR = nullptr, *dC = nullptr;
+    std::vector<unsigned char> hL, hR;
+    bool has_host = false;
+    // transpose scratch for role A / role B
+    DeviceBuffer tbufA, tbufB;
+    TransposeParams tpA{}, tpB{};
+    // SIMT tables
+    DeviceBuffer tables;
+    SimtParams simt{};
+    // UMMA
+    UmmaParams umma{};
+    CUtensorMap tmA{}, tmB{};
+    DeviceBuffer status;
+    // stage timing
+    bool stage_timing = false;
+    cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool ev_valid = false;
+    int64_t kernels_per_launch = 0;
+
+    ~tcontb_run()
+    {
+        for (auto& e : ev)
+            if (e) cudaEventDestroy(e);
+    }
+    const void* roleA_src() const { return plan.prob.swapped ? dR : dL; }
+    const void* roleB_src() const { return plan.prob.swapped ? dL : dR; }
+};
+
+namespace {
+
+void fill_operand_dev(const UmmaOperand& o, UmmaOperandDev* d)
+{
+    d->major = o.major;
+    d->slab_w = o.slab_w;
+    d->slabs_per_tile = o.slabs_per_tile;
+    d->n_row_digits = o.n_row_digits;
+    d->slab_bytes = o.slab_bytes;
+    for (int i = 0; i < kMaxTmaRank; ++i) {
+        d->row_digit_dim[i] = i < o.n_row_digits ? o.row_digit_dim[i] : -1;
+        d->row_digit_ext[i] = i < o.n_row_digits ? static_cast<int>(o.row_digit_ext[i]) : 1;
+        d->row_digit_cstride[i] = i < o.n_row_digits ? o.row_digit_cstride[i] : 0;
+    }
+    d->row_elem_cstride = o.row_elem_cstride;
+    d->slab_mode_ext = static_cast<int>(o.slab_mode_ext);
+    d->total_slabs = o.total_slabs;
+    for (int i = 0; i < 3; ++i) d->k_digit_dim[i] = o.k_digit_dim[i];
+}
+
+tcontb_status encode_map(const UmmaOperand& o, const void* base, CUtensorMap* out)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(TCONTB_RUNTIME_ERROR, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+    cuuint64_t dims[kMaxTmaRank];
+    cuuint64_t strides[kMaxTmaRank - 1];
+    cuuint32_t box[kMaxTmaRank], estr[kMaxTmaRank];
+    for (int d = 0; d < kMaxTmaRank; ++d) {
+        dims[d] = static_cast<cuuint64_t>(o.ext[d]);
+        box[d] = static_cast<cuuint32_t>(o.box[d]);
+        estr[d] = 1;
+        if (d > 0) strides[d - 1] = static_cast<cuuint64_t>(o.stride[d]) * 4u;
+    }
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, kMaxTmaRank, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TCONTB_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+    return TCONTB_OK;
+}
+
+// Device-side set-up shared by the three run constructors; dL/dR/dC must already be set.
+tcontb_status finish_run(tcontb_run* run)
+{
+    const Plan& pl = run->plan;
+    const Problem& p = pl.prob;
+    TC_CUDA(cudaGetDevice(&run->device));
+    TC_CUDA(cudaDeviceGetAttribute(&run->num_sms, cudaDevAttrMultiProcessorCount, run->device));
+    int major = 0;
+    TC_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, run->device));
+    if (major != 10) return fail(TCONTB_RUNTIME_ERROR, "this library holds sm_100a kernels only; the current device is not a B200-class GPU");
+
+    const void* kA = run->roleA_src();
+    const void* kB = run->roleB_src();
+    run->kernels_per_launch = 1;
+    if (pl.tA.needed) {
+        if (!make_transpose_params(pl.tA.rank, pl.tA.src_extent, pl.tA.perm, &run->tpA)) return fail(TCONTB_RUNTIME_ERROR, "bad transpose plan for A");
+        TC_CUDA(run->tbufA.alloc(static_cast<size_t>(pl.tA.elements) * run->elt));
+        kA = run->tbufA.ptr;
+        run->kernels_per_launch++;
+    }
+    if (pl.tB.needed) {
+        if (!make_transpose_params(pl.tB.rank, pl.tB.src_extent, pl.tB.perm, &run->tpB)) return fail(TCONTB_RUNTIME_ERROR, "bad transpose plan for B");
+        TC_CUDA(run->tbufB.alloc(static_cast<size_t>(pl.tB.elements) * run->elt));
+        kB = run->tbufB.ptr;
+        run->kernels_per_launch++;
+    }
+    TC_CUDA(run->status.alloc(sizeof(int)));
+    TC_CUDA(cudaMemset(run->status.ptr, 0, sizeof(int)));
+
+    if (pl.kernel == KERNEL_UMMA_TF32) {
+        const UmmaSpec& u = pl.umma;
+        fill_operand_dev(u.a, &run->umma.a);
+        fill_operand_dev(u.b, &run->umma.b);
+        run->umma.BN = u.BN;
+        run->umma.BK = u.BK;
+        run->umma.stages = u.stages;
+        run->umma.n_k_digits = u.n_k_digits;
+        for (int i = 0; i < 3; ++i) run->umma.k_digit_ext[i] = static_cast<int>(u.k_digit_ext[i]);
+        run->umma.k_iters = static_cast<int>(u.k_iters);
+        run->umma.tiles_m = u.tiles_m;
+        run->umma.tiles_n = u.tiles_n;
+        run->umma.raster_group = u.raster_group;
+        run->umma.C = static_cast<float*>(run->dC);
+        run->umma.status = static_cast<int*>(run->status.ptr);
+        tcontb_status st = encode_map(u.a, kA, &run->tmA);
+        if (st != TCONTB_OK) return st;
+        st = encode_map(u.b, kB, &run->tmB);
+        if (st != TCONTB_OK) return st;
+        TC_CUDA(umma_tf32_configure(u.smem_bytes));
+    } else {
+        OffsetTables t;
+        build_offset_tables(p, &t);
+        const size_t n = t.offAm.size() + t.offAk.size() + t.offBn.size() + t.offBk.size() + t.offCm.size() + t.offCn.size();
+        std::vector<int64_t> flat;
+        flat.reserve(n);
+        size_t o[6];
+        const std::vector<int64_t>* src[6] = {&t.offAm, &t.offAk, &t.offBn, &t.offBk, &t.offCm, &t.offCn};
+        for (int i = 0; i < 6; ++i) {
+            o[i] = flat.size();
+            flat.insert(flat.end(), src[i]->begin(), src[i]->end());
+        }
+        TC_CUDA(run->tables.alloc(n * sizeof(int64_t)));
+        TC_CUDA(cudaMemcpy(run->tables.ptr, flat.data(), n * sizeof(int64_t), cudaMemcpyHostToDevice));
+        const int64_t* base = static_cast<const int64_t*>(run->tables.ptr);
+        run->simt.A = kA;
+        run->simt.B = kB;
+        run->simt.C = run->dC;
+        run->simt.M = p.Mtot;
+        run->simt.N = p.Ntot;
+        run->simt.K = p.Ktot;
+        run->simt.offAm = base + o[0];
+        run->simt.offAk = base + o[1];
+        run->simt.offBn = base + o[2];
+        run->simt.offBk = base + o[3];
+        run->simt.offCm = base + o[4];
+        run->simt.offCn = base + o[5];
+        run->simt.a_along_k = pl.simt.a_load_along_k;
+        run->simt.b_along_k = pl.simt.b_load_along_k;
+    }
+    const char* st_env = std::getenv("TCONT_STAGE_TIMES");
+    run->stage_timing = st_env && std::strcmp(st_env, "1") == 0;
+    if (run->stage_timing)
+        for (auto& e : run->ev) TC_CUDA(cudaEventCreate(&e));
+    return TCONTB_OK;
+}
+
+tcontb_status alloc_owned(tcontb_run* run)
+{
+    const Plan& pl = run->plan;
+    TC_CUDA(run->ownL.alloc(static_cast<size_t>(pl.sizeL) * run->elt));
+    TC_CUDA(run->ownR.alloc(static_cast<size_t>(pl.sizeR) * run->elt));
+    TC_CUDA(run->ownC.alloc(static_cast<size_t>(pl.sizeC) * run->elt));
+    run->dL = run->ownL.ptr;
+    run->dR = run->ownR.ptr;
+    run->dC = run->ownC.ptr;
+    TC_CUDA(cudaMemset(run->dC, 0, static_cast<size_t>(pl.sizeC) * run->elt));
+    return TCONTB_OK;
+}
+
+tcontb_status check_device()
+{
+    int n = 0;
+    const cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return fail(TCONTB_RUNTIME_ERROR, "no usable CUDA device (this engine has no CPU path)");
+    }
+    return TCONTB_OK;
+}
+
+tcontb_status new_run(const tcontb_plan* plan, std::unique_ptr<tcontb_run>* out)
+{
+    if (!plan) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionPlan is empty");
+    const tcontb_status st = check_device();
+    if (st != TCONTB_OK) return st;
+    out->reset(new tcontb_run());
+    (*out)->plan = plan->plan;
+    (*out)->elt = plan->plan.scalar_type == TCONTB_F64 ? 8 : 4;
+    return TCONTB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* tcontb_last_error(void) { return g_last_error.c_str(); }
+
+tcontb_status tcontb_plan_create(const tcontb_desc* d, tcontb_plan** out)
+{
+    if (!d || !out) return fail(TCONTB_INVALID_ARGUMENT, "Null descriptor or output pointer");
+    std::unique_ptr<tcontb_plan> pl(new tcontb_plan());
+    std::string err;
+    const int rc = make_plan(d->modeC, d->nC, d->modeA, d->nA, d->modeB, d->nB, d->op, d->scalar_type, d->ext_mode, d->ext_val,
+                             d->n_ext, d->backend_selection, load_cost_table(), &pl->plan, &err);
+    if (rc) return fail(static_cast<tcontb_status>(rc), err);
+    *out = pl.release();
+    return TCONTB_OK;
+}
+
+void tcontb_plan_destroy(tcontb_plan* plan) { delete plan; }
+
+int tcontb_plan_backend(const tcontb_plan* plan) { return plan ? plan->plan.backend : -1; }
+
+double tcontb_plan_flops(const tcontb_plan* plan) { return plan ? plan->plan.flops : 0.0; }
+
+tcontb_status tcontb_plan_describe(const tcontb_plan* plan, char* buf, size_t n)
+{
+    if (!plan || !buf || n == 0) return fail(TCONTB_INVALID_ARGUMENT, "Null plan or buffer");
+    const std::string s = describe_plan(plan->plan);
+    if (s.size() + 1 > n) return fail(TCONTB_INVALID_ARGUMENT, "Buffer too small for the plan description");
+    std::memcpy(buf, s.c_str(), s.size() + 1);
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_fill_uniform(void* dst, int scalar_type, int64_t n, uint64_t seed, uint64_t offset, double lo, double hi)
+{
+    if (!dst || n < 0 || (scalar_type != TCONTB_F32 && scalar_type != TCONTB_F64))
+        return fail(TCONTB_INVALID_ARGUMENT, "Bad arguments to tcontb_fill_uniform");
+    const uint64_t base = seed * 0x9E3779B97F4A7C15ull + offset;
+    for (int64_t i = 0; i < n; ++i) {
+        const double u = static_cast<double>(splitmix64(base + static_cast<uint64_t>(i)) >> 11) * (1.0 / 9007199254740992.0);
+        const double v = lo + (hi - lo) * u;
+        if (scalar_type == TCONTB_F64) static_cast<double*>(dst)[i] = v;
+        else static_cast<float*>(dst)[i] = static_cast<float>(v);
+    }
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_create_with_inputs(const tcontb_plan* plan, const void* a_host, const void* b_host, tcontb_run** out)
+{
+    if (!out) return fail(TCONTB_INVALID_ARGUMENT, "Null output pointer");
+    if (!a_host || !b_host) return fail(TCONTB_INVALID_ARGUMENT, "Null input buffer");
+    std::unique_ptr<tcontb_run> run;
+    tcontb_status st = new_run(plan, &run);
+    if (st != TCONTB_OK) return st;
+    const Plan& pl = run->plan;
+    const size_t bl = static_cast<size_t>(pl.sizeL) * run->elt, br = static_cast<size_t>(pl.sizeR) * run->elt;
+    run->hL.assign(static_cast<const unsigned char*>(a_host), static_cast<const unsigned char*>(a_host) + bl);
+    run->hR.assign(static_cast<const unsigned char*>(b_host), static_cast<const unsigned char*>(b_host) + br);
+    run->has_host = true;
+    st = alloc_owned(run.get());
+    if (st != TCONTB_OK) return st;
+    TC_CUDA(cudaMemcpy(run->dL, run->hL.data(), bl, cudaMemcpyHostToDevice));
+    TC_CUDA(cudaMemcpy(run->dR, run->hR.data(), br, cudaMemcpyHostToDevice));
+    st = finish_run(run.get());
+    if (st != TCONTB_OK) return st;
+    *out = run.release();
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_create(const tcontb_plan* plan, tcontb_run** out)
+{
+    if (!plan) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionPlan is empty");
+    if (!out) return fail(TCONTB_INVALID_ARGUMENT, "Null output pointer");
+    const Plan& pl = plan->plan;
+    const size_t elt = pl.scalar_type == TCONTB_F64 ? 8 : 4;
+    uint64_t seed = static_cast<uint64_t>(std::time(nullptr));
+    if (const char* s = std::getenv("TCONT_SEED")) seed = std::strtoull(s, nullptr, 10);
+    double lo = 0.0, hi = 1.0;
+    if (const char* r = std::getenv("TCONT_INPUT_RANGE")) {
+        if (std::sscanf(r, "%lf:%lf", &lo, &hi) != 2) return fail(TCONTB_INVALID_ARGUMENT, "TCONT_INPUT_RANGE must look like lo:hi");
+    }
+    std::vector<unsigned char> a(static_cast<size_t>(pl.sizeL) * elt), b(static_cast<size_t>(pl.sizeR) * elt);
+    tcontb_fill_uniform(a.data(), pl.scalar_type, pl.sizeL, seed, 0, lo, hi);
+    tcontb_fill_uniform(b.data(), pl.scalar_type, pl.sizeR, seed, static_cast<uint64_t>(pl.sizeL), lo, hi);
+    return tcontb_run_create_with_inputs(plan, a.data(), b.data(), out);
+}
+
+tcontb_status tcontb_run_create_on_device(const tcontb_plan* plan, const void* a_dev, const void* b_dev, void* c_dev,
+                                          tcontb_run** out)
+{
+    if (!out) return fail(TCONTB_INVALID_ARGUMENT, "Null output pointer");
+    if (!a_dev || !b_dev || !c_dev) return fail(TCONTB_INVALID_ARGUMENT, "Null device buffer");
+    if ((reinterpret_cast<uintptr_t>(a_dev) | reinterpret_cast<uintptr_t>(b_dev) | reinterpret_cast<uintptr_t>(c_dev)) & 15)
+        return fail(TCONTB_INVALID_ARGUMENT, "Device buffers must be 16-byte aligned");
+    std::unique_ptr<tcontb_run> run;
+    tcontb_status st = new_run(plan, &run);
+    if (st != TCONTB_OK) return st;
+    run->dL = const_cast<void*>(a_dev);
+    run->dR = const_cast<void*>(b_dev);
+    run->dC = c_dev;
+    st = finish_run(run.get());
+    if (st != TCONTB_OK) return st;
+    *out = run.release();
+    return TCONTB_OK;
+}
+
+void tcontb_run_destroy(tcontb_run* run) { delete run; }
+
+tcontb_status tcontb_run_set_stream(tcontb_run* run, void* cuda_stream)
+{
+    if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    run->stream = static_cast<cudaStream_t>(cuda_stream);
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_upload_inputs(tcontb_run* run, const void* a_host, const void* b_host)
+{
+    if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    if (!a_host || !b_host) return fail(TCONTB_INVALID_ARGUMENT, "Null input buffer");
+    const Plan& pl = run->plan;
+    TC_CUDA(cudaMemcpyAsync(run->dL, a_host, static_cast<size_t>(pl.sizeL) * run->elt, cudaMemcpyHostToDevice, run->stream));
+    TC_CUDA(cudaMemcpyAsync(run->dR, b_host, static_cast<size_t>(pl.sizeR) * run->elt, cudaMemcpyHostToDevice, run->stream));
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_launch(tcontb_run* run)
+{
+    if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    const Plan& pl = run->plan;
+    const bool t = run->stage_timing;
+    if (t) TC_CUDA(cudaEventRecord(run->ev[0], run->stream));
+    if (pl.tA.needed) TC_CUDA(launch_transpose(run->roleA_src(), run->tbufA.ptr, run->tpA, static_cast<int>(run->elt), run->stream));
+    if (t) TC_CUDA(cudaEventRecord(run->ev[1], run->stream));
+    if (pl.tB.needed) TC_CUDA(launch_transpose(run->roleB_src(), run->tbufB.ptr, run->tpB, static_cast<int>(run->elt), run->stream));
+    if (t) TC_CUDA(cudaEventRecord(run->ev[2], run->stream));
+    if (pl.kernel == KERNEL_UMMA_TF32)
+        TC_CUDA(launch_umma_tf32(run->umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
+    else
+        TC_CUDA(launch_simt_contract(run->simt, pl.scalar_type, run->stream));
+    if (t) {
+        TC_CUDA(cudaEventRecord(run->ev[3], run->stream));
+        run->ev_valid = true;
+    }
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_warmup(tcontb_run* run, int iterations)
+{
+    if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    for (int i = 0; i < iterations; ++i) {
+        const tcontb_status st = tcontb_run_launch(run);
+        if (st != TCONTB_OK) return st;
+    }
+    TC_CUDA(cudaDeviceSynchronize());
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_zero_output(tcontb_run* run)
+{
+    if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    TC_CUDA(cudaMemsetAsync(run->dC, 0, static_cast<size_t>(run->plan.sizeC) * run->elt, run->stream));
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_stage_times(tcontb_run* run, float out[6])
+{
+    if (!run || !out) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    for (int i = 0; i < 6; ++i) out[i] = 0.0f;
+    if (!run->stage_timing || !run->ev_valid) return TCONTB_OK;
+    TC_CUDA(cudaEventSynchronize(run->ev[3]));
+    float ta = 0, tb = 0, tc = 0;
+    TC_CUDA(cudaEventElapsedTime(&ta, run->ev[0], run->ev[1]));
+    TC_CUDA(cudaEventElapsedTime(&tb, run->ev[1], run->ev[2]));
+    TC_CUDA(cudaEventElapsedTime(&tc, run->ev[2], run->ev[3]));
+    out[0] = 1.0f;
+    out[1] = ta + tb + tc;
+    out[2] = run->plan.prob.swapped ? tb : ta;  // reported per caller operand: left, right
+    out[3] = run->plan.prob.swapped ? ta : tb;
+    out[4] = tc;
+    out[5] = 0.0f;  // C is written in its final order by the contraction kernel
+    return TCONTB_OK;
+}
+
+const void* tcontb_run_host_input(const tcontb_run* run, int which)
+{
+    if (!run || !run->has_host) return nullptr;
+    return which == 0 ? static_cast<const void*>(run->hL.data()) : static_cast<const void*>(run->hR.data());
+}
+
+tcontb_status tcontb_run_copy_output(tcontb_run* run, void* dst, size_t bytes)
+{
+    if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    if (!dst) return fail(TCONTB_INVALID_ARGUMENT, "Destination buffer is null");
+    const size_t have = static_cast<size_t>(run->plan.sizeC) * run->elt;
+    if (bytes > have) return fail(TCONTB_INVALID_ARGUMENT, "Requested more bytes than the output tensor holds");
+    TC_CUDA(cudaMemcpyAsync(dst, run->dC, bytes, cudaMemcpyDeviceToHost, run->stream));
+    TC_CUDA(cudaStreamSynchronize(run->stream));
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_time_launches(tcontb_run* run, int iterations, float* elapsed_ms, int64_t* kernel_launches)
+{
+    if (!run || !elapsed_ms || iterations <= 0) return fail(TCONTB_INVALID_ARGUMENT, "Bad arguments to tcontb_run_time_launches");
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    TC_CUDA(cudaEventCreate(&e0));
+    TC_CUDA(cudaEventCreate(&e1));
+    tcontb_status st = TCONTB_OK;
+    cudaError_t ce = cudaEventRecord(e0, run->stream);
+    for (int i = 0; i < iterations && st == TCONTB_OK && ce == cudaSuccess; ++i) st = tcontb_run_launch(run);
+    if (ce == cudaSuccess) ce = cudaEventRecord(e1, run->stream);
+    if (ce == cudaSuccess) ce = cudaEventSynchronize(e1);
+    if (ce == cudaSuccess) ce = cudaEventElapsedTime(elapsed_ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (st != TCONTB_OK) return st;
+    if (ce != cudaSuccess) return fail(TCONTB_RUNTIME_ERROR, std::string("CUDA error while timing launches: ") + cudaGetErrorString(ce));
+    if (kernel_launches) *kernel_launches = run->kernels_per_launch * iterations;
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_contract_host(tcontb_run* run, const void* a_host, const void* b_host, void* c_host, int64_t* h2d,
+                                       int64_t* d2h)
+{
+    if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    if (!c_host) return fail(TCONTB_INVALID_ARGUMENT, "Destination buffer is null");
+    tcontb_status st = tcontb_run_upload_inputs(run, a_host, b_host);
+    if (st != TCONTB_OK) return st;
+    st = tcontb_run_launch(run);
+    if (st != TCONTB_OK) return st;
+    const size_t cb = static_cast<size_t>(run->plan.sizeC) * run->elt;
+    st = tcontb_run_copy_output(run, c_host, cb);
+    if (st != TCONTB_OK) return st;
+    if (h2d) *h2d = (run->plan.sizeL + run->plan.sizeR) * static_cast<int64_t>(run->elt);
+    if (d2h) *d2h = static_cast<int64_t>(cb);
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_device_status(tcontb_run* run, int* status)
+{
+    if (!run || !status) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    TC_CUDA(cudaMemcpyAsync(status, run->status.ptr, sizeof(int), cudaMemcpyDeviceToHost, run->stream));
+    TC_CUDA(cudaStreamSynchronize(run->stream));
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_transpose(const void* src, void* dst, int rank, const int64_t* src_extent, const int* perm, int elem_bytes,
+                               void* cuda_stream)
+{
+    if (!src || !dst || !src_extent || !perm) return fail(TCONTB_INVALID_ARGUMENT, "Null argument to tcontb_transpose");
+    if (elem_bytes != 4 && elem_bytes != 8) return fail(TCONTB_INVALID_ARGUMENT, "Element size must be 4 or 8 bytes");
+    const tcontb_status st = check_device();
+    if (st != TCONTB_OK) return st;
+    TransposeParams tp{};
+    if (!make_transpose_params(rank, src_extent, perm, &tp)) return fail(TCONTB_INVALID_ARGUMENT, "Not a permutation, or a non-positive extent");
+    TC_CUDA(launch_transpose(src, dst, tp, elem_bytes, static_cast<cudaStream_t>(cuda_stream)));
+    return TCONTB_OK;
+}
+
+}  // extern "C"

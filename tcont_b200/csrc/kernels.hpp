@@ -1,0 +1,69 @@
+// kernels.hpp -- host-callable launchers of the sm_100a kernels (implemented in the .cu files).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "planner.hpp"
+
+namespace tcontb {
+
+// ---- generic SIMT contraction (simt_contract.cu) -----------------------------------------
+// GEMM view with offset tables: C[offCm[m] + offCn[n]] = sum_k A[offAm[m] + offAk[k]] * B[offBn[n] + offBk[k]].
+struct SimtParams {
+    const void* A;
+    const void* B;
+    void* C;
+    int64_t M, N, K;
+    const int64_t* offAm;
+    const int64_t* offAk;
+    const int64_t* offBn;
+    const int64_t* offBk;
+    const int64_t* offCm;
+    const int64_t* offCn;
+    int a_along_k, b_along_k;
+};
+cudaError_t launch_simt_contract(const SimtParams& p, int scalar_type, cudaStream_t stream);
+
+// ---- FP64 tensor-core contraction (dmma_f64.cu), same GEMM view ----------------------------
+cudaError_t launch_dmma_contract(const SimtParams& p, cudaStream_t stream);
+
+// ---- tensor permutation (transpose.cu) ------------------------------------------------------
+struct TransposeParams {
+    int rank;                      // after merging, <= kMaxModes
+    int64_t ext[kMaxModes];        // source extents
+    int64_t src_stride[kMaxModes]; // element strides of source mode i in the source
+    int64_t dst_stride[kMaxModes]; // element strides of source mode i in the destination
+    int64_t elements;
+};
+// Builds merged params for dst mode i = src mode perm[i]; returns false for a bad permutation.
+bool make_transpose_params(int rank, const int64_t* src_extent, const int* perm, TransposeParams* out);
+cudaError_t launch_transpose(const void* src, void* dst, const TransposeParams& p, int elem_bytes, cudaStream_t stream);
+
+// ---- TF32 tcgen05 contraction (umma_tf32.cu) -------------------------------------------------
+struct UmmaOperandDev {
+    int major, slab_w, slabs_per_tile, n_row_digits, slab_bytes;
+    int row_digit_dim[kMaxTmaRank];
+    int row_digit_ext[kMaxTmaRank];
+    long long row_digit_cstride[kMaxTmaRank];
+    long long row_elem_cstride;
+    int slab_mode_ext;
+    long long total_slabs;
+    int k_digit_dim[3];
+};
+struct UmmaParams {
+    UmmaOperandDev a, b;
+    int BN, BK, stages, n_k_digits;
+    int k_digit_ext[3];
+    int k_iters;
+    long long tiles_m, tiles_n;
+    int raster_group;
+    float* C;
+    int* status;  // device status word: set non-zero when a bounded wait gives up
+};
+// tmapA / tmapB are 128-byte CUtensorMap objects passed by value as kernel parameters.
+cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,
+                             cudaStream_t stream);
+cudaError_t umma_tf32_configure(int smem_bytes);
+
+}  // namespace tcontb

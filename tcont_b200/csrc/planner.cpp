@@ -1,0 +1,576 @@
+// planner.cpp -- see planner.hpp.
+#include "planner.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <sstream>
+
+namespace tcontb {
+namespace {
+
+int find_char(const std::string& s, char c)
+{
+    const size_t p = s.find(c);
+    return p == std::string::npos ? -1 : static_cast<int>(p);
+}
+
+bool has_duplicates(const std::string& s)
+{
+    for (size_t i = 0; i < s.size(); ++i)
+        for (size_t j = i + 1; j < s.size(); ++j)
+            if (s[i] == s[j]) return true;
+    return false;
+}
+
+int index_of(const std::vector<int>& v, int x)
+{
+    for (size_t i = 0; i < v.size(); ++i)
+        if (v[i] == x) return static_cast<int>(i);
+    return -1;
+}
+
+int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Builds the kernel-facing problem from mode strings of C, left and right.
+// Returns 0 / 1 (invalid) / 3 (unsupported).
+int build_problem(const std::string& mC, const std::string& mL, const std::string& mR, const std::string& ext_mode,
+                  const std::vector<int64_t>& ext_val, int scalar_type, Problem* out, std::string* err)
+{
+    Problem p;
+    p.scalar_type = scalar_type;
+    auto extent_of = [&](char c) -> int64_t {
+        const int i = find_char(ext_mode, c);
+        return i < 0 ? -1 : ext_val[static_cast<size_t>(i)];
+    };
+    for (const std::string* s : {&mC, &mL, &mR}) {
+        for (char c : *s) {
+            const int64_t e = extent_of(c);
+            if (e < 0) {
+                *err = std::string("Missing extent for mode: ") + c;
+                return 1;
+            }
+            if (e == 0) {
+                *err = std::string("Extent of mode '") + c + "' must be positive";
+                return 1;
+            }
+        }
+        if (has_duplicates(*s)) {
+            *err = "A mode appears twice in one tensor (traces/diagonals are not expressible)";
+            return 3;
+        }
+    }
+    // C's stride-1 mode decides which caller operand plays role A.
+    p.swapped = !mC.empty() && find_char(mL, mC[0]) < 0 && find_char(mR, mC[0]) >= 0;
+    const std::string& mA = p.swapped ? mR : mL;
+    const std::string& mB = p.swapped ? mL : mR;
+
+    std::string all;
+    for (char c : mC + mA + mB)
+        if (find_char(all, c) < 0) all.push_back(c);
+    for (char c : all) {
+        const bool inC = find_char(mC, c) >= 0, inA = find_char(mA, c) >= 0, inB = find_char(mB, c) >= 0;
+        Mode m;
+        m.names = std::string(1, c);
+        m.extent = extent_of(c);
+        if (inC && inA && inB) {
+            *err = std::string("Mode '") + c + "' is in C, A and B: batch modes are not supported (the reference rejects them too)";
+            return 3;
+        }
+        if (inC && !inA && !inB) {
+            *err = std::string("Mode '") + c + "' of C is in neither input";
+            return 3;
+        }
+        if (!inC && inA != inB) {
+            *err = std::string("Mode '") + c + "' is in one input only and not in C (free reductions are not supported)";
+            return 3;
+        }
+        m.group = inC ? (inA ? GROUP_M : GROUP_N) : GROUP_K;
+        p.modes.push_back(m);
+    }
+    auto ids = [&](const std::string& s) {
+        std::vector<int> v;
+        for (char c : s) v.push_back(find_char(all, c));
+        return v;
+    };
+    p.A = ids(mA);
+    p.B = ids(mB);
+    p.C = ids(mC);
+
+    // Fuse y into x when y follows x immediately in every tensor that holds them.
+    bool fused = true;
+    while (fused) {
+        fused = false;
+        for (size_t x = 0; x < p.modes.size() && !fused; ++x) {
+            for (size_t y = 0; y < p.modes.size() && !fused; ++y) {
+                if (x == y || p.modes[x].group != p.modes[y].group) continue;
+                if (p.modes[x].extent == 0 || p.modes[y].extent == 0) continue;
+                bool ok = true;
+                for (std::vector<int>* t : {&p.A, &p.B, &p.C}) {
+                    const int ix = index_of(*t, static_cast<int>(x)), iy = index_of(*t, static_cast<int>(y));
+                    if ((ix < 0) != (iy < 0)) ok = false;
+                    else if (ix >= 0 && iy != ix + 1) ok = false;
+                }
+                if (!ok) continue;
+                p.modes[x].names += p.modes[y].names;
+                p.modes[x].extent *= p.modes[y].extent;
+                p.modes[y].extent = 0;  // tombstone
+                for (std::vector<int>* t : {&p.A, &p.B, &p.C}) {
+                    const int iy = index_of(*t, static_cast<int>(y));
+                    if (iy >= 0) t->erase(t->begin() + iy);
+                }
+                fused = true;
+            }
+        }
+    }
+    auto set_strides = [&](const std::vector<int>& t, int which, int64_t* total) {
+        int64_t s = 1;
+        for (int id : t) {
+            Mode& m = p.modes[static_cast<size_t>(id)];
+            (which == 0 ? m.sA : which == 1 ? m.sB : m.sC) = s;
+            s *= m.extent;
+        }
+        *total = s;
+    };
+    set_strides(p.A, 0, &p.sizeA);
+    set_strides(p.B, 1, &p.sizeB);
+    set_strides(p.C, 2, &p.sizeC);
+
+    for (int id : p.C) {
+        if (p.modes[static_cast<size_t>(id)].group == GROUP_M) p.M.push_back(id);
+        else p.N.push_back(id);
+    }
+    // K order: follow the operand whose stride-1 mode is contracted, so that operand's loads
+    // run along memory; A decides when both or neither are.
+    const bool a_kfirst = !p.A.empty() && p.modes[static_cast<size_t>(p.A[0])].group == GROUP_K;
+    const bool b_kfirst = !p.B.empty() && p.modes[static_cast<size_t>(p.B[0])].group == GROUP_K;
+    const std::vector<int>& korder = (!a_kfirst && b_kfirst) ? p.B : p.A;
+    for (int id : korder)
+        if (p.modes[static_cast<size_t>(id)].group == GROUP_K) p.K.push_back(id);
+    for (int id : p.M) p.Mtot *= p.modes[static_cast<size_t>(id)].extent;
+    for (int id : p.N) p.Ntot *= p.modes[static_cast<size_t>(id)].extent;
+    for (int id : p.K) p.Ktot *= p.modes[static_cast<size_t>(id)].extent;
+    *out = p;
+    return 0;
+}
+
+// Fills one operand's staging description. `t` = tensor mode list, `rows` = its row modes in C
+// order, `tile_rows` = 128 for A, BN for B.
+bool stage_operand(const Problem& p, const std::vector<int>& t, const std::vector<int>& rows, bool is_a, int kc_mode,
+                   int BK, UmmaOperand* o, std::string* why)
+{
+    o->rank = static_cast<int>(t.size());
+    for (int d = 0; d < kMaxTmaRank; ++d) {
+        o->ext[d] = 1;
+        o->box[d] = 1;
+        o->stride[d] = 0;
+    }
+    int64_t s = 1;
+    for (int d = 0; d < o->rank; ++d) {
+        const Mode& m = p.modes[static_cast<size_t>(t[static_cast<size_t>(d)])];
+        o->ext[d] = m.extent;
+        o->stride[d] = s;
+        s *= m.extent;
+        if (m.extent >= (int64_t(1) << 31)) {
+            *why = "a mode extent does not fit a TMA dimension";
+            return false;
+        }
+    }
+    for (int d = o->rank; d < kMaxTmaRank; ++d) o->stride[d] = s;  // padded unit dims
+    if (s * 4 >= (int64_t(1) << 40)) {
+        *why = "tensor too large for TMA strides";
+        return false;
+    }
+    if (o->rank >= 2 && (o->ext[0] % 4) != 0) {
+        *why = "stride-1 extent is not a multiple of 16 bytes (TMA global strides)";
+        return false;
+    }
+    const int first = t[0];
+    o->major = p.modes[static_cast<size_t>(first)].group == GROUP_K ? 0 : 1;
+    o->kc_dim = index_of(t, kc_mode);
+    int slab_mode;
+    if (o->major == 1) {
+        slab_mode = first;
+        o->slab_w = 32;
+    } else {
+        if (first != kc_mode) {
+            *why = "K-major operand whose stride-1 mode is not the chunked K mode";
+            return false;
+        }
+        slab_mode = rows[0];
+        o->slab_w = 8;  // refined by the caller once the tile height is known
+    }
+    o->slab_dim = index_of(t, slab_mode);
+    const Mode& sm = p.modes[static_cast<size_t>(slab_mode)];
+    o->slab_mode_ext = sm.extent;
+    o->row_elem_cstride = sm.sC;
+    (void)is_a;
+    (void)BK;
+    return true;
+}
+
+void finish_operand(const Problem& p, const std::vector<int>& t, const std::vector<int>& rows, int tile_rows, int BK,
+                    const std::vector<int>& kdigits, UmmaOperand* o)
+{
+    if (o->major == 0) {
+        // K-major: rows per slab = the largest power of two (8..tile height) that pads the slab
+        // mode by at most 15 %; failing that, the one that pads least.
+        int best = 8;
+        double best_waste = 1e30;
+        for (int w = 8; w <= tile_rows && w <= 256; w *= 2) {
+            const double waste = double(ceil_div(o->slab_mode_ext, w) * w) / double(o->slab_mode_ext);
+            const bool ok = waste <= 1.15, best_ok = best_waste <= 1.15;
+            if ((ok && (!best_ok || w > best)) || (!ok && !best_ok && waste < best_waste - 1e-12)) {
+                best = w;
+                best_waste = waste;
+            }
+        }
+        if (tile_rows / best > 16) best = tile_rows / 16;  // at most 16 slabs per operand tile
+        o->slab_w = best;
+    }
+    o->slabs_per_tile = tile_rows / o->slab_w;
+    const int slab_mode = t[static_cast<size_t>(o->slab_dim)];
+    o->n_row_digits = 0;
+    o->row_digit_dim[0] = o->slab_dim;
+    o->row_digit_ext[0] = ceil_div(o->slab_mode_ext, o->slab_w);
+    o->row_digit_cstride[0] = o->row_elem_cstride * o->slab_w;
+    o->n_row_digits = 1;
+    o->total_slabs = o->row_digit_ext[0];
+    for (int id : rows) {
+        if (id == slab_mode) continue;
+        const Mode& m = p.modes[static_cast<size_t>(id)];
+        const int n = o->n_row_digits++;
+        o->row_digit_dim[n] = index_of(t, id);
+        o->row_digit_ext[n] = m.extent;
+        o->row_digit_cstride[n] = m.sC;
+        o->total_slabs *= m.extent;
+    }
+    for (int i = 0; i < 3; ++i)
+        o->k_digit_dim[i] = i < static_cast<int>(kdigits.size()) ? index_of(t, kdigits[static_cast<size_t>(i)]) : -1;
+    if (o->major == 1) {
+        o->box[o->slab_dim] = 32;
+        o->box[o->kc_dim] = BK;
+        o->slab_bytes = BK * 128;
+    } else {
+        o->box[o->kc_dim] = 32;
+        o->box[o->slab_dim] = o->slab_w;
+        o->slab_bytes = o->slab_w * 128;
+    }
+}
+
+void plan_umma(const Problem& p, UmmaSpec* u)
+{
+    u->eligible = false;
+    if (p.scalar_type != 0) { u->why_not = "not Float32"; return; }
+    if (const char* k = std::getenv("TCONT_KERNEL")) {
+        // Debug switch: TCONT_KERNEL=simt keeps Float32 contractions on the CUDA-core kernel.
+        if (std::strcmp(k, "simt") == 0) { u->why_not = "disabled by TCONT_KERNEL=simt"; return; }
+    }
+    if (p.A.size() < 2 || p.B.size() < 2 || p.A.size() > kMaxTmaRank || p.B.size() > kMaxTmaRank) {
+        u->why_not = "operand rank outside 2..5 after fusion";
+        return;
+    }
+    if (p.M.empty() || p.N.empty() || p.K.empty() || p.K.size() > 3) {
+        u->why_not = "needs M, N and 1..3 K modes";
+        return;
+    }
+    const bool a_kmajor = p.modes[static_cast<size_t>(p.A[0])].group == GROUP_K;
+    const bool b_kmajor = p.modes[static_cast<size_t>(p.B[0])].group == GROUP_K;
+    int kc;
+    if (a_kmajor && b_kmajor) {
+        if (p.A[0] != p.B[0]) { u->why_not = "both operands K-major on different modes"; return; }
+        kc = p.A[0];
+    } else if (a_kmajor) kc = p.A[0];
+    else if (b_kmajor) kc = p.B[0];
+    else kc = p.K[0];
+    const int64_t kc_ext = p.modes[static_cast<size_t>(kc)].extent;
+    int BK = 32;
+    if (!a_kmajor && !b_kmajor) BK = kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32;
+    u->BK = BK;
+    std::vector<int> kdigits{kc};
+    for (int id : p.K)
+        if (id != kc) kdigits.push_back(id);
+    u->n_k_digits = static_cast<int>(kdigits.size());
+    u->k_iters = 1;
+    for (int i = 0; i < 3; ++i) u->k_digit_ext[i] = 1;
+    for (size_t i = 0; i < kdigits.size(); ++i) {
+        const int64_t e = p.modes[static_cast<size_t>(kdigits[i])].extent;
+        u->k_digit_ext[i] = i == 0 ? ceil_div(e, BK) : e;
+        u->k_iters *= u->k_digit_ext[i];
+    }
+    if (!stage_operand(p, p.A, p.M, true, kc, BK, &u->a, &u->why_not)) return;
+    if (!stage_operand(p, p.B, p.N, false, kc, BK, &u->b, &u->why_not)) return;
+
+    u->BM = 128;
+    finish_operand(p, p.A, p.M, u->BM, BK, kdigits, &u->a);
+    u->tiles_m = ceil_div(u->a.total_slabs, u->a.slabs_per_tile);
+    // N tile: the widest of 256/128/64/32 that is not wider than the (padded) N extent needs and
+    // still yields at least one tile per SM; otherwise the narrowest admissible one.
+    int bn = 32;
+    {
+        UmmaOperand probe = u->b;
+        finish_operand(p, p.B, p.N, 32, BK, kdigits, &probe);
+        const int64_t padded = probe.total_slabs * probe.slab_w;
+        int widest = 32;
+        while (widest < 256 && widest < padded) widest *= 2;
+        bn = widest;
+        for (int cand = widest; cand >= 32; cand /= 2) {
+            UmmaOperand tmp = u->b;
+            finish_operand(p, p.B, p.N, cand, BK, kdigits, &tmp);
+            if (tmp.slabs_per_tile < 1) break;
+            bn = cand;
+            if (u->tiles_m * ceil_div(tmp.total_slabs, tmp.slabs_per_tile) >= 148) break;
+        }
+    }
+    u->BN = bn;
+    finish_operand(p, p.B, p.N, u->BN, BK, kdigits, &u->b);
+    if (u->b.slabs_per_tile < 1 || u->a.slabs_per_tile + u->b.slabs_per_tile > 32) {
+        u->why_not = "too many slabs per stage";
+        return;
+    }
+    u->tiles_n = ceil_div(u->b.total_slabs, u->b.slabs_per_tile);
+    const int stage_bytes = u->a.slabs_per_tile * u->a.slab_bytes + u->b.slabs_per_tile * u->b.slab_bytes;
+    const int budget = 227 * 1024 - 8 * 1024;
+    u->stages = std::max(2, std::min(8, budget / stage_bytes));
+    u->smem_bytes = u->stages * stage_bytes + 8 * 1024 + 1024;
+    u->raster_group = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(u->tiles_m,
+                      std::llround(std::sqrt(148.0 * u->BN / u->BM)))));
+    u->eligible = true;
+}
+
+std::string perm_modes(const Problem& p, const std::vector<int>& ids)
+{
+    std::string s;
+    for (int id : ids) s += p.modes[static_cast<size_t>(id)].names;
+    return s;
+}
+
+void fill_transpose(const std::string& src, const std::string& dst, const std::string& ext_mode,
+                    const std::vector<int64_t>& ext_val, TransposeSpec* t)
+{
+    t->needed = src != dst;
+    t->rank = static_cast<int>(src.size());
+    t->elements = 1;
+    for (size_t i = 0; i < src.size(); ++i) {
+        t->src_extent[i] = ext_val[static_cast<size_t>(find_char(ext_mode, src[i]))];
+        t->elements *= t->src_extent[i];
+        t->perm[i] = find_char(src, dst[i]);
+    }
+}
+
+double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const CostTable& c)
+{
+    const double elt = p.scalar_type == 1 ? 8.0 : 4.0;
+    const double flops = 2.0 * double(p.Mtot) * double(p.Ntot) * double(p.Ktot);
+    double c_bytes = double(p.sizeC) * elt;
+    double rate = p.scalar_type == 1 ? c.simt_f64_tflops : c.simt_f32_tflops;
+    if (kernel == KERNEL_UMMA_TF32) {
+        rate = c.umma_tf32_tflops;
+        // rows of a slab that are not contiguous in C cost a 32-byte sector per element
+        if (u.a.row_elem_cstride != 1) c_bytes *= 8.0;
+    }
+    const double bytes = (double(p.sizeA) + double(p.sizeB)) * elt + c_bytes;
+    return c.launch_us + std::max(flops / (rate * 1e6), bytes / (c.hbm_gbs * 1e3));
+}
+
+}  // namespace
+
+CostTable load_cost_table()
+{
+    CostTable c;
+    const char* path = std::getenv("TCONT_COST_TABLE");
+    if (!path) return c;
+    std::ifstream f(path);
+    std::string key;
+    double v;
+    // "key value" pairs, one per line; unknown keys are ignored.
+    while (f >> key >> v) {
+        if (key == "hbm_gbs") c.hbm_gbs = v;
+        else if (key == "umma_tf32_tflops") c.umma_tf32_tflops = v;
+        else if (key == "simt_f32_tflops") c.simt_f32_tflops = v;
+        else if (key == "simt_f64_tflops") c.simt_f64_tflops = v;
+        else if (key == "launch_us") c.launch_us = v;
+    }
+    return c;
+}
+
+int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* modeB, int nB, char op, int scalar_type,
+              const char* ext_mode, const int64_t* ext_val, int n_ext, int backend_selection, const CostTable& cost,
+              Plan* plan, std::string* err)
+{
+    if (!plan || !err) return 1;
+    if (nC < 0 || nA < 0 || nB < 0 || n_ext < 0 || nC > kMaxModes || nA > kMaxModes || nB > kMaxModes || n_ext > 64) {
+        *err = "Mode counts out of range";
+        return 1;
+    }
+    if ((nC && !modeC) || (nA && !modeA) || (nB && !modeB) || (n_ext && (!ext_mode || !ext_val))) {
+        *err = "Null mode or extent array";
+        return 1;
+    }
+    if (scalar_type != 0 && scalar_type != 1) {
+        *err = "Unsupported scalar type";
+        return 1;
+    }
+    if (backend_selection < 0 || backend_selection > 2) {
+        *err = "Unknown backend selection";
+        return 1;
+    }
+    if (nA == 0 || nB == 0 || nC == 0) {
+        *err = "Each tensor needs at least one mode";
+        return 1;
+    }
+    Plan pl;
+    pl.modeC.assign(modeC, static_cast<size_t>(nC));
+    pl.modeA.assign(modeA, static_cast<size_t>(nA));
+    pl.modeB.assign(modeB, static_cast<size_t>(nB));
+    pl.ext_mode.assign(ext_mode, static_cast<size_t>(n_ext));
+    pl.ext_val.assign(ext_val, ext_val + n_ext);
+    pl.op = op;
+    pl.scalar_type = scalar_type;
+    pl.backend_selection = backend_selection;
+
+    Problem direct;
+    int rc = build_problem(pl.modeC, pl.modeA, pl.modeB, pl.ext_mode, pl.ext_val, scalar_type, &direct, err);
+    if (rc) return rc;
+    if (direct.sizeA >= (int64_t(1) << 32) || direct.sizeB >= (int64_t(1) << 32)) {
+        *err = "Input tensors with 2^32 or more elements are not supported";
+        return 3;
+    }
+    auto count = [&](const std::string& s) {
+        int64_t n = 1;
+        for (char c : s) n *= pl.ext_val[static_cast<size_t>(find_char(pl.ext_mode, c))];
+        return n;
+    };
+    pl.sizeL = count(pl.modeA);
+    pl.sizeR = count(pl.modeB);
+    pl.sizeC = count(pl.modeC);
+    pl.flops = 2.0 * std::sqrt(double(pl.sizeL) * double(pl.sizeR) * double(pl.sizeC));
+
+    UmmaSpec direct_umma;
+    plan_umma(direct, &direct_umma);
+    const int direct_kernel = direct_umma.eligible ? KERNEL_UMMA_TF32 : KERNEL_SIMT;
+    pl.est_direct_us = contraction_us(direct, direct_kernel, direct_umma, cost);
+
+    // Transpose-assisted candidate: role A becomes [M modes in C order | K modes], role B becomes
+    // [N modes in C order | K modes]; C is written in its final order by the contraction kernel,
+    // so there is no third transpose (the reference's TTGT always pays C' -> C,
+    // backends/ttgt_cutt/src/ttgt_cutt.cpp:811-816).
+    const std::string& roleA_src = direct.swapped ? pl.modeB : pl.modeA;
+    const std::string& roleB_src = direct.swapped ? pl.modeA : pl.modeB;
+    const std::string kmodes = perm_modes(direct, direct.K);
+    const std::string roleA_dst = perm_modes(direct, direct.M) + kmodes;
+    const std::string roleB_dst = perm_modes(direct, direct.N) + kmodes;
+    Problem ttgt;
+    rc = build_problem(pl.modeC, roleA_dst, roleB_dst, pl.ext_mode, pl.ext_val, scalar_type, &ttgt, err);
+    if (rc) return rc;
+    UmmaSpec ttgt_umma;
+    plan_umma(ttgt, &ttgt_umma);
+    const int ttgt_kernel = ttgt_umma.eligible ? KERNEL_UMMA_TF32 : KERNEL_SIMT;
+    TransposeSpec tA, tB;
+    fill_transpose(roleA_src, roleA_dst, pl.ext_mode, pl.ext_val, &tA);
+    fill_transpose(roleB_src, roleB_dst, pl.ext_mode, pl.ext_val, &tB);
+    const double elt = scalar_type == 1 ? 8.0 : 4.0;
+    double t_us = 0;
+    if (tA.needed) t_us += cost.launch_us + 2.0 * double(tA.elements) * elt / (cost.hbm_gbs * 0.7 * 1e3);
+    if (tB.needed) t_us += cost.launch_us + 2.0 * double(tB.elements) * elt / (cost.hbm_gbs * 0.7 * 1e3);
+    pl.est_ttgt_us = t_us + contraction_us(ttgt, ttgt_kernel, ttgt_umma, cost);
+
+    bool use_ttgt;
+    if (backend_selection == 1) use_ttgt = false;
+    else if (backend_selection == 2) use_ttgt = true;
+    else use_ttgt = (tA.needed || tB.needed) && pl.est_ttgt_us < pl.est_direct_us;
+
+    if (use_ttgt) {
+        pl.backend = 1;
+        pl.prob = ttgt;
+        pl.prob.swapped = direct.swapped;  // roles still map to the caller's operands as in `direct`
+        pl.tA = tA;
+        pl.tB = tB;
+        pl.kernel = ttgt_kernel;
+        pl.umma = ttgt_umma;
+    } else {
+        pl.backend = 0;
+        pl.prob = direct;
+        pl.kernel = direct_kernel;
+        pl.umma = direct_umma;
+    }
+    const Problem& p = pl.prob;
+    auto first_is = [&](const std::vector<int>& t, const std::vector<int>& grp) {
+        return !t.empty() && !grp.empty() && t[0] == grp[0];
+    };
+    // SIMT loads run along m (or n) when the operand's stride-1 mode is the fastest mode of the
+    // flat m (n) index, along k when it is the fastest contracted mode.
+    pl.simt.a_load_along_k = first_is(p.A, p.M) ? 0 : (first_is(p.A, p.K) ? 1 : 0);
+    pl.simt.b_load_along_k = first_is(p.B, p.N) ? 0 : (first_is(p.B, p.K) ? 1 : 0);
+    *plan = pl;
+    return 0;
+}
+
+void build_offset_tables(const Problem& p, OffsetTables* t)
+{
+    auto fill = [&](const std::vector<int>& grp, int64_t total, int which, std::vector<int64_t>* out) {
+        out->assign(static_cast<size_t>(total), 0);
+        for (int64_t i = 0; i < total; ++i) {
+            int64_t rem = i, off = 0;
+            for (int id : grp) {
+                const Mode& m = p.modes[static_cast<size_t>(id)];
+                const int64_t idx = rem % m.extent;
+                rem /= m.extent;
+                off += idx * (which == 0 ? m.sA : which == 1 ? m.sB : m.sC);
+            }
+            (*out)[static_cast<size_t>(i)] = off;
+        }
+    };
+    fill(p.M, p.Mtot, 0, &t->offAm);
+    fill(p.K, p.Ktot, 0, &t->offAk);
+    fill(p.N, p.Ntot, 1, &t->offBn);
+    fill(p.K, p.Ktot, 1, &t->offBk);
+    fill(p.M, p.Mtot, 2, &t->offCm);
+    fill(p.N, p.Ntot, 2, &t->offCn);
+}
+
+std::string describe_plan(const Plan& pl)
+{
+    std::ostringstream o;
+    const Problem& p = pl.prob;
+    auto list = [&](const std::vector<int>& ids) {
+        std::string s = "[";
+        for (size_t i = 0; i < ids.size(); ++i) {
+            const Mode& m = p.modes[static_cast<size_t>(ids[i])];
+            s += (i ? "," : "") + std::string("\"") + m.names + ":" + std::to_string(m.extent) + "\"";
+        }
+        return s + "]";
+    };
+    auto perm = [&](const TransposeSpec& t) {
+        std::string s = "[";
+        for (int i = 0; i < t.rank; ++i) s += (i ? "," : "") + std::to_string(t.perm[i]);
+        return s + "]";
+    };
+    o << "{\"backend\":\"" << (pl.backend == 0 ? "direct" : "ttgt") << "\",\"kernel\":\""
+      << (pl.kernel == KERNEL_UMMA_TF32 ? "umma_tf32" : pl.kernel == KERNEL_DMMA_F64 ? "dmma_f64" : "simt") << "\""
+      << ",\"scalar\":\"" << (pl.scalar_type == 1 ? "f64" : "f32") << "\",\"swapped\":" << (p.swapped ? "true" : "false")
+      << ",\"A\":" << list(p.A) << ",\"B\":" << list(p.B) << ",\"C\":" << list(p.C) << ",\"M\":" << list(p.M)
+      << ",\"N\":" << list(p.N) << ",\"K\":" << list(p.K) << ",\"Mtot\":" << p.Mtot << ",\"Ntot\":" << p.Ntot
+      << ",\"Ktot\":" << p.Ktot << ",\"transpose_a\":" << (pl.tA.needed ? perm(pl.tA) : "null")
+      << ",\"transpose_b\":" << (pl.tB.needed ? perm(pl.tB) : "null") << ",\"est_direct_us\":" << pl.est_direct_us
+      << ",\"est_ttgt_us\":" << pl.est_ttgt_us << ",\"simt\":{\"a_along_k\":" << pl.simt.a_load_along_k
+      << ",\"b_along_k\":" << pl.simt.b_load_along_k << "}";
+    const UmmaSpec& u = pl.umma;
+    o << ",\"umma\":{\"eligible\":" << (u.eligible ? "true" : "false");
+    if (!u.eligible) o << ",\"why_not\":\"" << u.why_not << "\"";
+    else {
+        o << ",\"BM\":" << u.BM << ",\"BN\":" << u.BN << ",\"BK\":" << u.BK << ",\"stages\":" << u.stages
+          << ",\"k_iters\":" << u.k_iters << ",\"tiles_m\":" << u.tiles_m << ",\"tiles_n\":" << u.tiles_n
+          << ",\"a_major\":\"" << (u.a.major ? "MN" : "K") << "\",\"b_major\":\"" << (u.b.major ? "MN" : "K") << "\""
+          << ",\"a_slab_w\":" << u.a.slab_w << ",\"b_slab_w\":" << u.b.slab_w << ",\"a_slabs\":" << u.a.slabs_per_tile
+          << ",\"b_slabs\":" << u.b.slabs_per_tile << ",\"smem_bytes\":" << u.smem_bytes
+          << ",\"coalesced_store\":" << (u.a.row_elem_cstride == 1 ? "true" : "false");
+    }
+    o << "}}";
+    return o.str();
+}
+
+}  // namespace tcontb

@@ -1,0 +1,134 @@
+// planner.hpp -- host-side planning of one tensor contraction (no CUDA dependency).
+//
+// Stands where the reference has three pieces: the LightGBM backend selector
+// (src/backend_model_selector.cpp:365-403), the Python COGENT planner
+// (backends/cogent/plan/tc_plan.py:5-98 and base/*.py) and the TTGT permutation search
+// (backends/ttgt_cutt/src/ttgt_cutt.cpp:220-687).  The plan is a pure function of the
+// descriptor and the cost table, so it can be unit-tested without a GPU.
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+
+namespace tcontb {
+
+constexpr int kMaxModes = 16;
+constexpr int kMaxTmaRank = 5;
+
+enum ModeGroup { GROUP_M = 0, GROUP_N = 1, GROUP_K = 2 };
+enum KernelKind { KERNEL_SIMT = 0, KERNEL_UMMA_TF32 = 1, KERNEL_DMMA_F64 = 2 };
+
+struct Mode {
+    std::string names;  // the caller's mode letters fused into this mode, fastest first
+    int64_t extent = 1;
+    int64_t sA = 0, sB = 0, sC = 0;  // element strides (0 = mode absent from that tensor)
+    int group = GROUP_K;
+};
+
+// The contraction the kernels see: roles A/B may be exchanged relative to the caller's
+// left/right operands so that the M group always owns C's stride-1 mode (the reference makes
+// the same exchange through its swap_flag, backends/cogent/plan/tc_gen_inner_group.py:450, but
+// keyed on the letter "a"; here it is keyed on position).
+struct Problem {
+    int scalar_type = 1;
+    bool swapped = false;
+    std::vector<Mode> modes;
+    std::vector<int> A, B, C;  // mode ids in memory order, fastest first
+    std::vector<int> M, N, K;  // M and N in C's order; K in the order the kernels iterate it
+    int64_t Mtot = 1, Ntot = 1, Ktot = 1;
+    int64_t sizeA = 1, sizeB = 1, sizeC = 1;
+};
+
+// A permutation of one caller tensor: dst mode i = src mode perm[i].
+struct TransposeSpec {
+    bool needed = false;
+    int rank = 0;
+    int64_t src_extent[kMaxModes] = {0};
+    int perm[kMaxModes] = {0};
+    int64_t elements = 0;
+};
+
+// How one operand's tile is staged into shared memory for tcgen05.mma: a tile is a run of
+// "slabs", each slab one 2-D TMA box (rows x 128 bytes, 128-byte swizzle).
+struct UmmaOperand {
+    int rank = 0;
+    int64_t ext[kMaxTmaRank] = {1, 1, 1, 1, 1};
+    int64_t stride[kMaxTmaRank] = {0, 0, 0, 0, 0};  // elements
+    int box[kMaxTmaRank] = {1, 1, 1, 1, 1};
+    int major = 0;         // 0: K-major (stride-1 mode is the chunked K mode), 1: MN-major
+    int slab_w = 32;       // rows (K-major) or contiguous elements (MN-major) of the slab mode per slab
+    int slab_dim = 0;      // tensor dim the slab runs along
+    int kc_dim = 0;        // tensor dim of the chunked K mode
+    int slabs_per_tile = 4;
+    int n_row_digits = 1;  // slab index = mixed radix number; digit 0 = chunk of the slab mode
+    int row_digit_dim[kMaxTmaRank] = {0};
+    int64_t row_digit_ext[kMaxTmaRank] = {1};
+    int64_t row_digit_cstride[kMaxTmaRank] = {0};  // C offset per unit of the digit
+    int64_t row_elem_cstride = 1;                  // C stride of one element inside a slab
+    int64_t slab_mode_ext = 1;
+    int64_t total_slabs = 1;
+    int k_digit_dim[3] = {-1, -1, -1};
+    int slab_bytes = 0;
+};
+
+struct UmmaSpec {
+    bool eligible = false;
+    std::string why_not;
+    int BM = 128, BN = 256, BK = 32, stages = 4;
+    UmmaOperand a, b;
+    int n_k_digits = 1;
+    int64_t k_digit_ext[3] = {1, 1, 1};  // digit 0 = chunks of the chunked K mode
+    int64_t k_iters = 1, tiles_m = 1, tiles_n = 1;
+    int raster_group = 16;
+    int smem_bytes = 0;
+};
+
+struct SimtSpec {
+    int a_load_along_k = 0;  // 0: threads run along m when loading A (m contiguous), 1: along k
+    int b_load_along_k = 0;
+    int tile = 64;           // BM = BN
+};
+
+struct CostTable {
+    // Measured on B200 (see profiles/); overridable through the file named by TCONT_COST_TABLE.
+    double hbm_gbs = 6546.9;
+    double umma_tf32_tflops = 600.0;
+    double simt_f32_tflops = 20.0;
+    double simt_f64_tflops = 15.0;
+    double launch_us = 3.0;
+};
+
+struct Plan {
+    // caller's descriptor, owned copies
+    std::string modeC, modeA, modeB, ext_mode;
+    std::vector<int64_t> ext_val;
+    char op = '?';
+    int scalar_type = 1;
+    int backend_selection = 0;
+
+    int backend = 0;        // TCONTB_BACKEND_*
+    Problem prob;           // what the contraction kernel sees (after the transposes, if any)
+    TransposeSpec tA, tB;   // transposes feeding role A / role B (src = the caller's tensor of that role)
+    int kernel = KERNEL_SIMT;
+    SimtSpec simt;
+    UmmaSpec umma;
+    double est_direct_us = 0, est_ttgt_us = 0;
+    double flops = 0;
+    int64_t sizeL = 1, sizeR = 1, sizeC = 1;  // caller's left, right, output element counts
+};
+
+// Returns 0 (ok), 1 (invalid argument), 3 (unsupported); `err` receives the message.
+int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* modeB, int nB, char op, int scalar_type,
+              const char* ext_mode, const int64_t* ext_val, int n_ext, int backend_selection, const CostTable& cost,
+              Plan* plan, std::string* err);
+
+std::string describe_plan(const Plan& plan);
+CostTable load_cost_table();
+
+// Offset tables of the GEMM view: address(A, m, k) = offAm[m] + offAk[k] and so on.
+struct OffsetTables {
+    std::vector<int64_t> offAm, offAk, offBn, offBk, offCm, offCn;
+};
+void build_offset_tables(const Problem& p, OffsetTables* t);
+
+}  // namespace tcontb

@@ -1,0 +1,197 @@
+// transpose.cu -- tensor permutation through a padded shared-memory tile, 16-byte vectors on
+// both the read and the write side.
+//
+// Replaces the cuTT kernels the reference's TTGT route calls (external/cutt/src/cuttkernel.cu:
+// transposeTiled :38-118, transposePacked :123-222, transposeTiledCopy :356-426).  It keeps
+// cuTT's two ideas -- merge ranks that stay adjacent (external/cutt/src/cuttplan.cpp:63-126) and
+// stage the (input-contiguous x output-contiguous) plane through shared memory -- but moves
+// 16-byte vectors, uses 64-bit offsets, and is selected by the planner rather than by timing
+// every candidate in prepare().
+#include <algorithm>
+
+#include "kernels.hpp"
+
+namespace tcontb {
+
+bool make_transpose_params(int rank, const int64_t* src_extent, const int* perm, TransposeParams* out)
+{
+    if (rank < 1 || rank > kMaxModes) return false;
+    bool seen[kMaxModes] = {false};
+    for (int i = 0; i < rank; ++i) {
+        if (perm[i] < 0 || perm[i] >= rank || seen[perm[i]] || src_extent[i] <= 0) return false;
+        seen[perm[i]] = true;
+    }
+    int64_t dst_stride_of_src[kMaxModes];
+    int64_t s = 1;
+    for (int i = 0; i < rank; ++i) {
+        dst_stride_of_src[perm[i]] = s;
+        s *= src_extent[perm[i]];
+    }
+    // Merge source modes j, j+1 that are also neighbours (same order) in the destination.
+    int pos_in_dst[kMaxModes];
+    for (int i = 0; i < rank; ++i) pos_in_dst[perm[i]] = i;
+    int n = 0;
+    int64_t st = 1;
+    for (int j = 0; j < rank; ++j) {
+        if (n > 0 && pos_in_dst[j] == pos_in_dst[j - 1] + 1) {
+            out->ext[n - 1] *= src_extent[j];
+        } else {
+            out->ext[n] = src_extent[j];
+            out->src_stride[n] = st;
+            out->dst_stride[n] = dst_stride_of_src[j];
+            ++n;
+        }
+        st *= src_extent[j];
+    }
+    out->rank = n;
+    out->elements = st;
+    return true;
+}
+
+namespace {
+
+template <typename V>
+struct VecOf;
+
+constexpr int TILE = 64;
+
+struct TileGeom {
+    int d0;  // merged source mode that is fastest in the destination
+    int64_t tiles0, tiles1;
+};
+
+// Leading mode preserved: plain row copies, one vector per thread.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) permute_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, TransposeParams p)
+{
+    const int64_t vec_per_row = p.ext[0] / VEC;
+    const int64_t total = p.elements / VEC;
+    for (int64_t v = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; v < total; v += int64_t(gridDim.x) * blockDim.x) {
+        int64_t rem = v / vec_per_row;
+        const int64_t c = (v % vec_per_row) * VEC;
+        int64_t so = c, dof = c;
+        for (int i = 1; i < p.rank; ++i) {
+            const int64_t idx = rem % p.ext[i];
+            rem /= p.ext[i];
+            so += idx * p.src_stride[i];
+            dof += idx * p.dst_stride[i];
+        }
+        if constexpr (VEC == 1) {
+            dst[dof] = __ldg(src + so);
+        } else {
+            using V = typename VecOf<T>::type;
+            *reinterpret_cast<V*>(dst + dof) = __ldg(reinterpret_cast<const V*>(src + so));
+        }
+    }
+}
+
+template <>
+struct VecOf<float> {
+    using type = float4;
+};
+template <>
+struct VecOf<double> {
+    using type = double2;
+};
+
+// General case: a TILE x TILE plane over (source-fastest mode 0, destination-fastest mode d0)
+// goes through shared memory; the remaining modes are spread over the grid.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) permute_tiled_kernel(const T* __restrict__ src, T* __restrict__ dst, TransposeParams p,
+                                                            TileGeom g)
+{
+    __shared__ T tile[TILE][TILE + 1];
+    int64_t t = blockIdx.x;
+    const int64_t c0 = (t % g.tiles0) * TILE;  // offset along source mode 0
+    t /= g.tiles0;
+    const int64_t r0 = (t % g.tiles1) * TILE;  // offset along source mode d0
+    t /= g.tiles1;
+    int64_t sbase = 0, dbase = 0;
+    for (int i = 1; i < p.rank; ++i) {
+        if (i == g.d0) continue;
+        const int64_t idx = t % p.ext[i];
+        t /= p.ext[i];
+        sbase += idx * p.src_stride[i];
+        dbase += idx * p.dst_stride[i];
+    }
+    const int64_t e0 = p.ext[0], e1 = p.ext[g.d0];
+    const int64_t s1 = p.src_stride[g.d0];  // source stride of mode d0
+    const int64_t d0s = p.dst_stride[0];    // destination stride of source mode 0
+    constexpr int VPR = TILE / VEC;         // vectors per tile row
+
+    for (int idx = threadIdx.x; idx < TILE * VPR; idx += 256) {
+        const int r = idx / VPR, cv = (idx % VPR) * VEC;
+        if (r0 + r < e1 && c0 + cv < e0) {
+            const T* ptr = src + sbase + (r0 + r) * s1 + (c0 + cv);
+            if constexpr (VEC == 1) {
+                tile[r][cv] = __ldg(ptr);
+            } else {
+                using V = typename VecOf<T>::type;
+                const V v = __ldg(reinterpret_cast<const V*>(ptr));
+                const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+                for (int q = 0; q < VEC; ++q) tile[r][cv + q] = e[q];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < TILE * VPR; idx += 256) {
+        const int c = idx / VPR, rv = (idx % VPR) * VEC;
+        if (c0 + c < e0 && r0 + rv < e1) {
+            T* ptr = dst + dbase + (c0 + c) * d0s + (r0 + rv);
+            if constexpr (VEC == 1) {
+                *ptr = tile[rv][c];
+            } else {
+                using V = typename VecOf<T>::type;
+                V v;
+                T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+                for (int q = 0; q < VEC; ++q) e[q] = tile[rv + q][c];
+                *reinterpret_cast<V*>(ptr) = v;
+            }
+        }
+    }
+}
+
+template <typename T>
+cudaError_t launch_typed(const T* src, T* dst, const TransposeParams& p, cudaStream_t stream)
+{
+    constexpr int VMAX = 16 / sizeof(T);
+    if (p.elements == 0) return cudaSuccess;
+    const bool aligned = (reinterpret_cast<uintptr_t>(src) % 16 == 0) && (reinterpret_cast<uintptr_t>(dst) % 16 == 0);
+    // Find the merged source mode that is fastest in the destination.
+    int d0 = 0;
+    for (int i = 0; i < p.rank; ++i)
+        if (p.dst_stride[i] == 1) d0 = i;
+    if (d0 == 0) {
+        const bool vec = aligned && p.ext[0] % VMAX == 0;
+        const int64_t total = p.elements / (vec ? VMAX : 1);
+        const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+        if (vec) permute_rows_kernel<T, VMAX><<<blocks, 256, 0, stream>>>(src, dst, p);
+        else permute_rows_kernel<T, 1><<<blocks, 256, 0, stream>>>(src, dst, p);
+        return cudaGetLastError();
+    }
+    TileGeom g;
+    g.d0 = d0;
+    g.tiles0 = (p.ext[0] + TILE - 1) / TILE;
+    g.tiles1 = (p.ext[d0] + TILE - 1) / TILE;
+    int64_t blocks = g.tiles0 * g.tiles1;
+    for (int i = 1; i < p.rank; ++i)
+        if (i != d0) blocks *= p.ext[i];
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const bool vec = aligned && p.ext[0] % VMAX == 0 && p.ext[d0] % VMAX == 0;
+    if (vec) permute_tiled_kernel<T, VMAX><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, dst, p, g);
+    else permute_tiled_kernel<T, 1><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, dst, p, g);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_transpose(const void* src, void* dst, const TransposeParams& p, int elem_bytes, cudaStream_t stream)
+{
+    if (elem_bytes == 4) return launch_typed(static_cast<const float*>(src), static_cast<float*>(dst), p, stream);
+    if (elem_bytes == 8) return launch_typed(static_cast<const double*>(src), static_cast<double*>(dst), p, stream);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace tcontb

@@ -1,0 +1,425 @@
+// umma_tf32.cu -- direct TF32 contraction on the 5th-generation tensor cores (sm_100a only).
+//
+// One persistent CTA per SM, three roles:
+//   warp 0      TMA producer.  An operand tile is a run of "slabs"; each slab is one 2-D box of a
+//               5-D tensor map laid over the operand's own (strided, multi-mode) layout, written
+//               with the 128-byte swizzle so that it is already a UMMA canonical tile.  Lane i owns
+//               slab i and issues its own cp.async.bulk.tensor per K step (no cluster multicast).
+//   warp 1      allocates tensor memory, and its lane 0 issues tcgen05.mma kind::tf32
+//               (M = 128, N = BN, K = 8 per instruction) into one of two TMEM accumulators.
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (lane = row), scatter it to C's final,
+//               permuted position; with C's stride-1 mode on the slab rows a warp writes 128
+//               contiguous bytes per column.
+// Every wait is bounded: when one gives up the CTA raises a status word, stops issuing work,
+// lets the remaining loops run empty, waits (bounded) for its outstanding bulk copies, frees its
+// tensor memory and returns.
+//
+// Stands where the reference runs its generated TF32 WMMA kernels
+// (backends/cogent/plan/generators/kernels/kernel_compute.py:851-1833, kernel_load.py:687-868,
+// kernel_store.py:280-507): same contract (C overwritten with the fp32-accumulated TF32
+// products; raw fp32 bits are handed to the tensor core, which ignores the low mantissa bits).
+#include <cuda.h>
+
+#include "kernels.hpp"
+
+namespace tcontb {
+namespace {
+
+constexpr int kThreads = 192;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ unsigned long long global_timer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit passes, or
+// immediately when another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    if (*abort_flag) return false;
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 255u) {
+            if (*abort_flag) return false;
+            const unsigned long long now = global_timer();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2, int c3, int c4)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
+//   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
+//   bits 32-45 stride byte offset >> 4 bits 46-47 version      bits 61-63 layout (2 = 128 B swizzle)
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr >> 4) & 0x3fffu);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Raster order: groups of `g` tile rows are swept column by column, so the CTAs that run
+// together share A and B panels in L2.
+__device__ __forceinline__ void decode_tile(long long tile, long long tiles_m, long long tiles_n, int g, long long* tm, long long* tn)
+{
+    const long long per_group = static_cast<long long>(g) * tiles_n;
+    const long long group = tile / per_group;
+    const long long first_m = group * g;
+    const long long rows = (tiles_m - first_m) < g ? (tiles_m - first_m) : g;
+    const long long local = tile - group * per_group;
+    *tm = first_m + local % rows;
+    *tn = local / rows;
+}
+
+// Splits a slab index into its mixed-radix digits and returns the C offset of the slab start.
+// valid = false when the slab lies beyond the tensor.
+__device__ __forceinline__ long long slab_c_offset(const UmmaOperandDev& o, long long slab, int* digit0, bool* valid)
+{
+    *valid = slab < o.total_slabs;
+    long long rem = slab, off = 0;
+#pragma unroll
+    for (int d = 0; d < kMaxTmaRank; ++d) {
+        if (d < o.n_row_digits) {
+            const long long idx = rem % o.row_digit_ext[d];
+            rem /= o.row_digit_ext[d];
+            off += idx * o.row_digit_cstride[d];
+            if (d == 0) *digit0 = static_cast<int>(idx);
+        }
+    }
+    return off;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+                 const __grid_constant__ UmmaParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int SA = p.a.slabs_per_tile, SB = p.b.slabs_per_tile;
+    const uint32_t a_tile_bytes = static_cast<uint32_t>(SA * p.a.slab_bytes);
+    const uint32_t stage_bytes = a_tile_bytes + static_cast<uint32_t>(SB * p.b.slab_bytes);
+
+    uint8_t* aux = smem + static_cast<size_t>(p.stages) * stage_bytes;
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(aux);  // [8]
+    uint64_t* bar_empty = bar_full + 8;                     // [8]
+    uint64_t* bar_tfull = bar_empty + 8;                    // [2]
+    uint64_t* bar_tempty = bar_tfull + 2;                   // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    long long* col_off = reinterpret_cast<long long*>(aux + 256);  // [2][256], -1 = column not stored
+
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < static_cast<uint32_t>(2 * p.BN)) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(bar_full + s), 1);
+            mbar_init(smem_u32(bar_empty + s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(bar_tfull + a), 1);
+            mbar_init(smem_u32(bar_tempty + a), 128);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const long long total_tiles = p.tiles_m * p.tiles_n;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: lane i owns slab i of the stage ----------------
+        const bool is_a = lane < SA;
+        const bool active = lane < SA + SB;
+        const UmmaOperandDev& o = is_a ? p.a : p.b;
+        const void* tmap = is_a ? static_cast<const void*>(&tmapA) : static_cast<const void*>(&tmapB);
+        const int slab = is_a ? lane : lane - SA;
+        const uint32_t my_off = is_a ? static_cast<uint32_t>(slab * p.a.slab_bytes)
+                                     : a_tile_bytes + static_cast<uint32_t>(slab * p.b.slab_bytes);
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmapA)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmapB)) : "memory");
+        }
+        int stage = 0;
+        uint32_t phase = 0;
+        uint32_t issued_mask = 0, issued_parity = 0;
+        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            long long tm, tn;
+            decode_tile(tile, p.tiles_m, p.tiles_n, p.raster_group, &tm, &tn);
+            int base[kMaxTmaRank] = {0, 0, 0, 0, 0};
+            if (active) {
+                const long long s = (is_a ? tm * SA : tn * SB) + slab;
+                if (s < o.total_slabs) {
+                    long long rem = s;
+#pragma unroll
+                    for (int d = 0; d < kMaxTmaRank; ++d) {
+                        if (d < o.n_row_digits) {
+                            const int idx = static_cast<int>(rem % o.row_digit_ext[d]);
+                            rem /= o.row_digit_ext[d];
+                            const int v = d == 0 ? idx * o.slab_w : idx;
+#pragma unroll
+                            for (int t = 0; t < kMaxTmaRank; ++t)
+                                if (o.row_digit_dim[d] == t) base[t] = v;
+                        }
+                    }
+                } else {
+                    // Slab beyond the tensor: start the box past the slab mode's end, TMA fills zeros.
+#pragma unroll
+                    for (int t = 0; t < kMaxTmaRank; ++t)
+                        if (o.row_digit_dim[0] == t) base[t] = ((o.slab_mode_ext + 31) / 32) * 32;
+                }
+            }
+            int kd0 = 0, kd1 = 0, kd2 = 0;  // K digits: chunk of the chunked mode, then the other K modes
+            for (int it = 0; it < p.k_iters; ++it) {
+                const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + stage), phase ^ 1u, abort_flag));
+                if (ok) {
+                    if (lane == 0) mbar_arrive_expect_tx(smem_u32(bar_full + stage), stage_bytes);
+                    __syncwarp();
+                    if (active) {
+                        int c[kMaxTmaRank];
+#pragma unroll
+                        for (int t = 0; t < kMaxTmaRank; ++t) {
+                            c[t] = base[t];
+                            if (o.k_digit_dim[0] == t) c[t] = kd0 * p.BK;
+                            if (o.k_digit_dim[1] == t) c[t] = kd1;
+                            if (o.k_digit_dim[2] == t) c[t] = kd2;
+                        }
+                        tma_load_5d(smem_u32(smem + static_cast<size_t>(stage) * stage_bytes + my_off), tmap,
+                                    smem_u32(bar_full + stage), c[0], c[1], c[2], c[3], c[4]);
+                    }
+                    issued_mask |= 1u << stage;
+                    issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
+                }
+                if (++kd0 == p.k_digit_ext[0]) {
+                    kd0 = 0;
+                    if (++kd1 == p.k_digit_ext[1]) {
+                        kd1 = 0;
+                        ++kd2;
+                    }
+                }
+                if (++stage == p.stages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        if (*abort_flag && lane == 0) {
+            // Give the bulk copies this warp issued a bounded time to land before the CTA ends.
+            for (int s = 0; s < p.stages; ++s) {
+                if (!(issued_mask & (1u << s))) continue;
+                const unsigned long long t0 = global_timer();
+                while (!mbar_try_wait(smem_u32(bar_full + s), (issued_parity >> s) & 1u))
+                    if (global_timer() - t0 > 100000000ull) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(p.a.major) << 15) |
+                                   (static_cast<uint32_t>(p.b.major) << 16) | (static_cast<uint32_t>(p.BN >> 3) << 17) |
+                                   (static_cast<uint32_t>(128 >> 4) << 24);
+            // MN-major: slabs sit one leading-byte-offset apart, 8 K rows per MMA = 1024 bytes.
+            // K-major : 8-row groups sit 1024 bytes apart, 8 K elements per MMA = 32 bytes.
+            const uint32_t a_lbo = p.a.major ? static_cast<uint32_t>(p.a.slab_bytes) : 16u;
+            const uint32_t b_lbo = p.b.major ? static_cast<uint32_t>(p.b.slab_bytes) : 16u;
+            const uint32_t a_kstep = p.a.major ? 1024u : 32u;
+            const uint32_t b_kstep = p.b.major ? 1024u : 32u;
+            const int ksteps = p.BK / 8;
+            int stage = 0;
+            uint32_t phase = 0;
+            long long iter = 0;
+            for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+                const int acc = static_cast<int>(iter & 1);
+                const uint32_t acc_parity = static_cast<uint32_t>((iter >> 1) & 1);
+                bool ok = mbar_wait(smem_u32(bar_tempty + acc), acc_parity ^ 1u, abort_flag);
+                tcgen05_fence_after();
+                const uint32_t tmem_c = tmem_base + static_cast<uint32_t>(acc * p.BN);
+                for (int it = 0; it < p.k_iters; ++it) {
+                    ok = ok && mbar_wait(smem_u32(bar_full + stage), phase, abort_flag);
+                    if (ok) {
+                        tcgen05_fence_after();
+                        const uint32_t a_base = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
+                        const uint32_t b_base = a_base + a_tile_bytes;
+                        for (int kk = 0; kk < ksteps; ++kk) {
+                            const uint64_t da = smem_desc(a_base + kk * a_kstep, a_lbo, 1024u);
+                            const uint64_t db = smem_desc(b_base + kk * b_kstep, b_lbo, 1024u);
+                            umma_tf32(tmem_c, da, db, idesc, (it | kk) != 0 ? 1u : 0u);
+                        }
+                        umma_commit(smem_u32(bar_empty + stage));  // frees the stage once the MMAs have read it
+                    }
+                    if (++stage == p.stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(smem_u32(bar_tfull + acc));  // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue: 4 warps, warp w reads TMEM lanes 32*(w%4).. ----------------
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const int et = threadIdx.x - 64;
+        long long iter = 0;
+        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+            long long tm, tn;
+            decode_tile(tile, p.tiles_m, p.tiles_n, p.raster_group, &tm, &tn);
+            const int acc = static_cast<int>(iter & 1);
+            const uint32_t acc_parity = static_cast<uint32_t>((iter >> 1) & 1);
+            // this thread's row of C
+            bool row_ok;
+            int digit0 = 0;
+            const int a_slab = row / p.a.slab_w, a_in = row % p.a.slab_w;
+            long long row_off = slab_c_offset(p.a, tm * SA + a_slab, &digit0, &row_ok);
+            row_ok = row_ok && (digit0 * p.a.slab_w + a_in < p.a.slab_mode_ext);
+            row_off += a_in * p.a.row_elem_cstride;
+            // column table of this tile
+            long long* cols = col_off + acc * 256;
+            for (int j = et; j < p.BN; j += 128) {
+                bool col_ok;
+                int d0 = 0;
+                const int b_slab = j / p.b.slab_w, b_in = j % p.b.slab_w;
+                long long off = slab_c_offset(p.b, tn * SB + b_slab, &d0, &col_ok);
+                col_ok = col_ok && (d0 * p.b.slab_w + b_in < p.b.slab_mode_ext);
+                cols[j] = col_ok ? off + b_in * p.b.row_elem_cstride : -1;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const bool ok = mbar_wait(smem_u32(bar_tfull + acc), acc_parity, abort_flag);
+            tcgen05_fence_after();
+            if (ok) {
+                float* crow = p.C + row_off;
+                for (int c0 = 0; c0 < p.BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * p.BN + c0), v);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const long long co = cols[c0 + j];
+                            if (co >= 0) __stcs(crow + co, __uint_as_float(v[j]));
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            mbar_arrive(smem_u32(bar_tempty + acc));
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicMax(p.status, 1);
+}
+
+}  // namespace
+
+cudaError_t umma_tf32_configure(int smem_bytes)
+{
+    return cudaFuncSetAttribute(umma_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+}
+
+cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,
+                             cudaStream_t stream)
+{
+    const long long total = p.tiles_m * p.tiles_n;
+    if (total <= 0) return cudaErrorInvalidValue;
+    const unsigned grid = static_cast<unsigned>(total < num_sms ? total : num_sms);
+    umma_tf32_kernel<<<grid, kThreads, smem_bytes, stream>>>(*static_cast<const CUtensorMap*>(tmapA),
+                                                            *static_cast<const CUtensorMap*>(tmapB), p);
+    return cudaGetLastError();
+}
+
+}  // namespace tcontb

@@ -1,0 +1,92 @@
+"""CPU-only: the host-side planner behind TconT::plan, driven through the C ABI."""
+import pytest
+
+from cases import CONFIGS, fixture_contraction, golden_fixtures, to_equation
+
+
+def describe(engine, c, selection=0):
+    return engine.plan(to_equation(engine, c, selection)).describe()
+
+
+def test_mode_groups_and_fusion(engine):
+    d = describe(engine, CONFIGS["cfg3"][0])
+    assert d["A"] == ["a:48", "e:48", "ij:576"] and d["B"] == ["bc:2304", "e:48", "k:24"]
+    assert d["M"] == ["a:48", "ij:576"] and d["N"] == ["bc:2304", "k:24"] and d["K"] == ["e:48"]
+    assert (d["Mtot"], d["Ntot"], d["Ktot"]) == (27648, 55296, 48)
+    # cfg5's (a,b) are neighbours in C but split by e in A: nothing may fuse
+    d5 = describe(engine, CONFIGS["cfg5"][0])
+    assert d5["C"] == ["a:128", "b:128", "c:128", "d:128"]
+
+
+def test_roles_follow_position_not_names(engine):
+    # C's stride-1 mode lives in the right operand: roles are exchanged (the reference keys this
+    # on the letter 'a', backends/cogent/plan/tc_gen_inner_group.py:450)
+    eq = engine.TCEquation("xyz", "kz", "ykx", dict(x=8, y=4, z=6, k=5))
+    d = engine.plan(eq).describe()
+    assert d["swapped"] is True and d["M"][0].startswith("x") and d["K"] == ["k:5"]
+    eq2 = engine.TCEquation("xyz", "ykx", "kz", dict(x=8, y=4, z=6, k=5))
+    assert engine.plan(eq2).describe()["swapped"] is False
+
+
+def test_backend_selection_and_names(engine):
+    c = CONFIGS["cfg1"][0]
+    assert engine.plan(to_equation(engine, c, 1)).backend == engine.Backend.COGENT
+    p = engine.plan(to_equation(engine, c, 2))
+    assert p.backend == engine.Backend.TTGT_CUTT
+    d = p.describe()
+    # role A = A[a,e,b,f] -> [a,b | K], role B = B[f,d,e,c] -> [c,d | K]; C needs no transpose
+    assert d["transpose_a"] == [0, 2, 3, 1] and d["transpose_b"] == [3, 1, 0, 2]
+    assert d["A"] == ["ab:576", "fe:256"] and d["B"] == ["cd:576", "fe:256"]
+
+
+def test_configs_pick_the_intended_kernels(engine):
+    d2 = describe(engine, CONFIGS["cfg2"][0])
+    assert d2["backend"] == "direct" and d2["kernel"] == "umma_tf32"
+    u = d2["umma"]
+    assert (u["a_major"], u["b_major"], u["BN"], u["BK"], u["k_iters"]) == ("MN", "K", 256, 32, 32)
+    assert u["tiles_m"] * u["tiles_n"] == 2048 and u["coalesced_store"] and u["smem_bytes"] <= 227 * 1024
+    d4 = describe(engine, CONFIGS["cfg4"][0])
+    assert d4["backend"] == "ttgt" and d4["kernel"] == "umma_tf32" and d4["umma"]["BK"] == 8
+    assert d4["transpose_a"] == [3, 2, 0, 1] and d4["A"] == ["ab:2304", "e:48", "f:8"]
+    d5 = describe(engine, CONFIGS["cfg5"][0])
+    assert d5["kernel"] == "umma_tf32" and d5["umma"]["k_iters"] == 512
+    assert describe(engine, CONFIGS["cfg3"][0])["kernel"] == "simt"
+    assert describe(engine, CONFIGS["cfg1"][0])["kernel"] == "simt"
+
+
+def test_every_reference_pattern_plans(engine):
+    for fx in golden_fixtures():
+        c = fixture_contraction(fx)
+        for sel in (0, 1, 2):
+            d = describe(engine, c, sel)
+            assert d["Mtot"] * d["Ntot"] == c.size(c.modeC)
+            assert d["Mtot"] * d["Ktot"] == c.size(c.modeB if d["swapped"] else c.modeA)
+
+
+def test_plan_is_deterministic(engine):
+    c = CONFIGS["cfg4"][0]
+    assert describe(engine, c) == describe(engine, c)
+
+
+def test_error_conventions(engine):
+    E = engine.TCEquation
+    with pytest.raises(ValueError, match="Missing extent for mode: d"):     # std::invalid_argument, src/tcont.cpp:44
+        engine.plan(E("abc", "adc", "db", dict(a=2, b=2, c=2)))
+    with pytest.raises(ValueError):
+        engine.plan(E("ab", "ak", "kb", dict(a=2, b=0, k=2)))
+    with pytest.raises(NotImplementedError, match="batch"):
+        engine.plan(E("abn", "akn", "kbn", dict(a=2, b=2, k=2, n=2)))
+    with pytest.raises(NotImplementedError):
+        engine.plan(E("ab", "akx", "kb", dict(a=2, b=2, k=2, x=2)))
+    with pytest.raises(ValueError):
+        engine.launch(None)
+    with pytest.raises(ValueError, match="ExecutionPlan is empty"):
+        engine.prepare(None)
+
+
+def test_flop_count_is_the_reference_formula(engine):
+    c = CONFIGS["cfg2"][0]
+    p = engine.plan(to_equation(engine, c))
+    assert p.flops == pytest.approx(2.0 * 65536 * 1024 * 1024)
+    assert engine.compute_gflops(p.equation, 1.0) == pytest.approx(p.flops / 1e6)
+    assert engine.compute_gflops(p.equation, 0.0) == 0.0
