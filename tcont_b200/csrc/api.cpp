@@ -141,7 +141,10 @@ tcontb_status encode_map(const UmmaOperand& o, const void* base, CUtensorMap* ou
         if (d > 0) strides[d - 1] = static_cast<cuuint64_t>(o.stride[d]) * 4u;
     }
     const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, kMaxTmaRank, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          // an MN-major 32-bit operand must be swizzled in 32-byte units for tcgen05.mma
+                          o.major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TCONTB_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
     return TCONTB_OK;

@@ -3,7 +3,7 @@
 // One persistent CTA per SM, three roles:
 //   warp 0      TMA producer.  An operand tile is a run of "slabs"; each slab is one 2-D box of a
 //               5-D tensor map laid over the operand's own (strided, multi-mode) layout, written
-//               with the 128-byte swizzle so that it is already a UMMA canonical tile.  Lane i owns
+//               with a 128-byte swizzle so that it is already a UMMA canonical tile.  Lane i owns
 //               slab i and issues its own cp.async.bulk.tensor per K step (no cluster multicast).
 //   warp 1      allocates tensor memory, and its lane 0 issues tcgen05.mma kind::tf32
 //               (M = 128, N = BN, K = 8 per instruction) into one of two TMEM accumulators.
@@ -108,17 +108,20 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_c, uint64_t desc_a, uint
         : "memory");
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
+// Shared-memory matrix descriptor, descriptor version 1 (Blackwell).
 //   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
-//   bits 32-45 stride byte offset >> 4 bits 46-47 version      bits 61-63 layout (2 = 128 B swizzle)
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+//   bits 32-45 stride byte offset >> 4 bits 46-47 version      bits 61-63 layout type
+// Layout types used here: 2 = 128-byte swizzle in 16-byte units (K-major operands);
+// 1 = 128-byte swizzle in 32-byte units, the only layout the tensor core accepts for an MN-major
+// operand of a 32-bit type (TMA writes it with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type)
 {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((addr >> 4) & 0x3fffu);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
     d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+    d |= static_cast<uint64_t>(layout_type) << 61;
     return d;
 }
 
@@ -307,10 +310,13 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(p.a.major) << 15) |
                                    (static_cast<uint32_t>(p.b.major) << 16) | (static_cast<uint32_t>(p.BN >> 3) << 17) |
                                    (static_cast<uint32_t>(128 >> 4) << 24);
-            // MN-major: slabs sit one leading-byte-offset apart, 8 K rows per MMA = 1024 bytes.
+            // MN-major: slabs sit one leading-byte-offset apart; the 8 K rows of one MMA are two
+            //           4-row groups 512 bytes apart (stride byte offset), 1024 bytes per MMA.
             // K-major : 8-row groups sit 1024 bytes apart, 8 K elements per MMA = 32 bytes.
             const uint32_t a_lbo = p.a.major ? static_cast<uint32_t>(p.a.slab_bytes) : 16u;
             const uint32_t b_lbo = p.b.major ? static_cast<uint32_t>(p.b.slab_bytes) : 16u;
+            const uint32_t a_sbo = p.a.major ? 512u : 1024u, b_sbo = p.b.major ? 512u : 1024u;
+            const uint32_t a_type = p.a.major ? 1u : 2u, b_type = p.b.major ? 1u : 2u;
             const uint32_t a_kstep = p.a.major ? 1024u : 32u;
             const uint32_t b_kstep = p.b.major ? 1024u : 32u;
             const int ksteps = p.BK / 8;
@@ -330,8 +336,8 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                         const uint32_t a_base = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
                         const uint32_t b_base = a_base + a_tile_bytes;
                         for (int kk = 0; kk < ksteps; ++kk) {
-                            const uint64_t da = smem_desc(a_base + kk * a_kstep, a_lbo, 1024u);
-                            const uint64_t db = smem_desc(b_base + kk * b_kstep, b_lbo, 1024u);
+                            const uint64_t da = smem_desc(a_base + kk * a_kstep, a_lbo, a_sbo, a_type);
+                            const uint64_t db = smem_desc(b_base + kk * b_kstep, b_lbo, b_sbo, b_type);
                             umma_tf32(tmem_c, da, db, idesc, (it | kk) != 0 ? 1u : 0u);
                         }
                         umma_commit(smem_u32(bar_empty + stage));  // frees the stage once the MMAs have read it
