@@ -5,6 +5,7 @@ the C++ surface of include/tcont.hpp).  This package is the thin Python binding 
 and the benchmark; it mirrors the reference's names (TCEquation, plan, prepare, launch, warmup,
 zero_output, copy_output_to_host, compute_gflops).
 """
+from . import sharding  # noqa: F401
 from .api import (  # noqa: F401
     Backend,
     BackendSelection,
