@@ -141,6 +141,32 @@ tcontb_status tcontb_fill_uniform(void* dst, int scalar_type, int64_t n, uint64_
 tcontb_status tcontb_transpose(const void* src_dev, void* dst_dev, int rank, const int64_t* src_extent, const int* perm,
                                int elem_bytes, void* cuda_stream);
 
+/* ---- allocation-free contraction ------------------------------------------------------------
+ *
+ * No counterpart in the reference.  For callers that must not trigger a device allocation: a
+ * process whose own memory pool has claimed the whole GPU, or a latency-critical loop that cannot
+ * take the device-wide synchronisation of cudaMalloc.  One contraction C = A*B on the caller's
+ * DEVICE buffers, asynchronous on `cuda_stream`, computed by the CUDA-core kernel (FP64, or plain
+ * FP32 arithmetic for TCONTB_F32 -- not the TF32 tensor-core path).  It calls no cudaMalloc /
+ * cudaFree and no allocating library routine: the kernel's scratch (its offset tables) lives in
+ * a 4 MiB array built into the library, resident on every GPU that loads the library until the
+ * process exits.
+ *
+ *  - Limit: 2*(M+N+K) <= 524288, with M, N, K the products of the external-left, external-right
+ *    and contracted extents; larger contractions return TCONTB_UNSUPPORTED with a message that
+ *    states the need and the limit.  d->backend_selection is ignored (always the direct route).
+ *  - The first call on each device resolves the array's device address (cudaGetSymbolAddress);
+ *    make that first call outside any stream capture.
+ *  - All calls share the one array and it keeps the previous call's contents; every call
+ *    overwrites the part it uses before its kernel reads it.  Calls whose GPU work can overlap
+ *    (different streams, concurrent host threads) race on it: keep them on one stream or
+ *    serialise them yourself.
+ *  - Errors of this entry point are reported by tcontb_no_alloc_last_error().
+ */
+tcontb_status tcontb_contract_no_alloc(const tcontb_desc* desc, const void* a_dev, const void* b_dev, void* c_dev,
+                                       void* cuda_stream);
+const char* tcontb_no_alloc_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

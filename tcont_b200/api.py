@@ -88,6 +88,10 @@ _lib.tcontb_transpose.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c
                                   C.c_void_p]
 
 
+_lib.tcontb_contract_no_alloc.argtypes = [C.POINTER(_Desc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+_lib.tcontb_no_alloc_last_error.restype = C.c_char_p
+
+
 def _check(status: int):
     if status == 0:
         return
@@ -292,3 +296,24 @@ def transpose(src_ptr: int, dst_ptr: int, src_extent, perm, elem_bytes: int, cud
     ext = (C.c_int64 * r)(*[int(x) for x in src_extent])
     pm = (C.c_int * r)(*[int(x) for x in perm])
     _check(_lib.tcontb_transpose(C.c_void_p(src_ptr), C.c_void_p(dst_ptr), r, ext, pm, elem_bytes, C.c_void_p(cuda_stream)))
+
+
+def contract_no_alloc(desc: TCEquation, a_ptr: int, b_ptr: int, c_ptr: int, cuda_stream: int = 0):
+    """tcontb_contract_no_alloc: one contraction on caller-owned device buffers without any device
+    allocation (for callers whose memory pool owns the whole GPU, or that cannot take cudaMalloc's
+    synchronisation). Limited to 2*(M+N+K) <= 524288; calls share one built-in scratch array, so
+    keep them on one stream."""
+    modes = "".join(sorted(desc.extent))
+    vals = (C.c_int64 * max(1, len(modes)))(*[int(desc.extent[m]) for m in modes])
+    d = _Desc(len(desc.modeC), len(desc.modeA), len(desc.modeB), desc.modeC.encode(), desc.modeA.encode(),
+              desc.modeB.encode(), desc.op.encode()[:1] or b"?", int(desc.scalar_type), len(modes), modes.encode(), vals,
+              int(desc.backend_selection))
+    st = _lib.tcontb_contract_no_alloc(C.byref(d), C.c_void_p(a_ptr), C.c_void_p(b_ptr), C.c_void_p(c_ptr),
+                                       C.c_void_p(cuda_stream))
+    if st:
+        msg = (_lib.tcontb_no_alloc_last_error() or b"").decode()
+        if st == 1:
+            raise ValueError(msg)
+        if st == 3:
+            raise NotImplementedError(msg)
+        raise TcontError(msg)

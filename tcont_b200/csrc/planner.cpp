@@ -285,7 +285,14 @@ void plan_umma(const Problem& p, UmmaSpec* u)
         kc = p.A[0];
     } else if (a_kmajor) kc = p.A[0];
     else if (b_kmajor) kc = p.B[0];
-    else kc = p.K[0];
+    else {
+        kc = p.K[0];
+        // Tuning switch: TCONT_UMMA_KC=<mode letter> picks the contracted mode that is cut into
+        // BK-sized chunks when both operands are MN-major (any K mode is legal then).
+        if (const char* want = std::getenv("TCONT_UMMA_KC"))
+            for (int id : p.K)
+                if (p.modes[static_cast<size_t>(id)].names.find(want[0]) != std::string::npos) kc = id;
+    }
     const int64_t kc_ext = p.modes[static_cast<size_t>(kc)].extent;
     int BK = 32;
     if (!a_kmajor && !b_kmajor) BK = kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32;
