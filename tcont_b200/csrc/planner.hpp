@@ -74,6 +74,7 @@ struct UmmaOperand {
 struct UmmaSpec {
     bool eligible = false;
     std::string why_not;
+    std::string kc_names;  // the contracted mode that is cut into BK-sized chunks
     int BM = 128, BN = 256, BK = 32, stages = 4;
     UmmaOperand a, b;
     int n_k_digits = 1;

@@ -64,18 +64,42 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 
 // Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit passes, or
 // immediately when another thread of the CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr)
 {
-    if (*abort_flag) return false;
+    uint32_t v;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v)
+{
+    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_shared_s64(uint32_t addr, long long v)
+{
+    asm volatile("st.shared.b64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ long long ld_shared_s64(uint32_t addr)
+{
+    long long v;
+    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// Bounded wait.  The fast path is a bare try_wait; every 256 failed polls it looks at the CTA's
+// abort flag (shared-memory word at `abort_addr`) and at the clock.  Returns false, and raises the
+// flag, when the limit passes; returns false at once when another thread already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_addr)
+{
     unsigned long long t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 255u) == 255u) {
-            if (*abort_flag) return false;
+        if ((spin & 255u) == 255u || spin == 0) {
+            if (ld_shared_u32(abort_addr)) return false;
+            if (spin == 0) continue;
             const unsigned long long now = global_timer();
             if (t0 == 0) t0 = now;
             else if (now - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
+                st_shared_u32(abort_addr, 1u);
                 return false;
             }
         }
@@ -141,30 +165,32 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Raster order: groups of `g` tile rows are swept column by column, so the CTAs that run
-// together share A and B panels in L2.
-__device__ __forceinline__ void decode_tile(long long tile, long long tiles_m, long long tiles_n, int g, long long* tm, long long* tn)
+// together share A and B panels in L2.  Tile and slab counts fit 32 bits (the planner checks).
+__device__ __forceinline__ void decode_tile(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t g, uint32_t* tm, uint32_t* tn)
 {
-    const long long per_group = static_cast<long long>(g) * tiles_n;
-    const long long group = tile / per_group;
-    const long long first_m = group * g;
-    const long long rows = (tiles_m - first_m) < g ? (tiles_m - first_m) : g;
-    const long long local = tile - group * per_group;
+    const uint32_t per_group = g * tiles_n;
+    const uint32_t group = tile / per_group;
+    const uint32_t first_m = group * g;
+    const uint32_t rows = (tiles_m - first_m) < g ? (tiles_m - first_m) : g;
+    const uint32_t local = tile - group * per_group;
     *tm = first_m + local % rows;
     *tn = local / rows;
 }
 
 // Splits a slab index into its mixed-radix digits and returns the C offset of the slab start.
 // valid = false when the slab lies beyond the tensor.
-__device__ __forceinline__ long long slab_c_offset(const UmmaOperandDev& o, long long slab, int* digit0, bool* valid)
+__device__ __forceinline__ long long slab_c_offset(const UmmaOperandDev& o, uint32_t slab, int* digit0, bool* valid)
 {
-    *valid = slab < o.total_slabs;
-    long long rem = slab, off = 0;
+    *valid = slab < static_cast<uint32_t>(o.total_slabs);
+    uint32_t rem = slab;
+    long long off = 0;
 #pragma unroll
     for (int d = 0; d < kMaxTmaRank; ++d) {
         if (d < o.n_row_digits) {
-            const long long idx = rem % o.row_digit_ext[d];
-            rem /= o.row_digit_ext[d];
-            off += idx * o.row_digit_cstride[d];
+            const uint32_t e = static_cast<uint32_t>(o.row_digit_ext[d]);
+            const uint32_t idx = rem % e;
+            rem /= e;
+            off += static_cast<long long>(idx) * o.row_digit_cstride[d];
             if (d == 0) *digit0 = static_cast<int>(idx);
         }
     }
@@ -176,7 +202,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                  const __grid_constant__ UmmaParams p)
 {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // 1024-byte aligned
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int SA = p.a.slabs_per_tile, SB = p.b.slabs_per_tile;
     const uint32_t a_tile_bytes = static_cast<uint32_t>(SA * p.a.slab_bytes);
@@ -188,8 +214,8 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     uint64_t* bar_tfull = bar_empty + 8;                    // [2]
     uint64_t* bar_tempty = bar_tfull + 2;                   // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    long long* col_off = reinterpret_cast<long long*>(aux + 256);  // [2][256], -1 = column not stored
+    const uint32_t abort_flag = smem_u32(tmem_slot + 1);
+    const uint32_t col_off = smem_u32(aux + 256);  // long long [2][256], -1 = column not stored
 
     uint32_t tmem_cols = 32;
     while (tmem_cols < static_cast<uint32_t>(2 * p.BN)) tmem_cols <<= 1;
@@ -203,7 +229,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             mbar_init(smem_u32(bar_tfull + a), 1);
             mbar_init(smem_u32(bar_tempty + a), 128);
         }
-        *abort_flag = 0;
+        st_shared_u32(abort_flag, 0u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -217,7 +243,8 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const long long total_tiles = p.tiles_m * p.tiles_n;
+    const uint32_t tiles_m = static_cast<uint32_t>(p.tiles_m), tiles_n = static_cast<uint32_t>(p.tiles_n);
+    const uint32_t total_tiles = tiles_m * tiles_n;
 
     if (warp == 0) {
         // ---------------- TMA producer: lane i owns slab i of the stage ----------------
@@ -235,19 +262,20 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         int stage = 0;
         uint32_t phase = 0;
         uint32_t issued_mask = 0, issued_parity = 0;
-        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            long long tm, tn;
-            decode_tile(tile, p.tiles_m, p.tiles_n, p.raster_group, &tm, &tn);
+        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            uint32_t tm, tn;
+            decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &tm, &tn);
             int base[kMaxTmaRank] = {0, 0, 0, 0, 0};
             if (active) {
-                const long long s = (is_a ? tm * SA : tn * SB) + slab;
-                if (s < o.total_slabs) {
-                    long long rem = s;
+                const uint32_t s = (is_a ? tm * SA : tn * SB) + slab;
+                if (s < static_cast<uint32_t>(o.total_slabs)) {
+                    uint32_t rem = s;
 #pragma unroll
                     for (int d = 0; d < kMaxTmaRank; ++d) {
                         if (d < o.n_row_digits) {
-                            const int idx = static_cast<int>(rem % o.row_digit_ext[d]);
-                            rem /= o.row_digit_ext[d];
+                            const uint32_t e = static_cast<uint32_t>(o.row_digit_ext[d]);
+                            const int idx = static_cast<int>(rem % e);
+                            rem /= e;
                             const int v = d == 0 ? idx * o.slab_w : idx;
 #pragma unroll
                             for (int t = 0; t < kMaxTmaRank; ++t)
@@ -295,7 +323,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                 }
             }
         }
-        if (*abort_flag && lane == 0) {
+        if (ld_shared_u32(abort_flag) && lane == 0) {
             // Give the bulk copies this warp issued a bounded time to land before the CTA ends.
             for (int s = 0; s < p.stages; ++s) {
                 if (!(issued_mask & (1u << s))) continue;
@@ -323,7 +351,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             int stage = 0;
             uint32_t phase = 0;
             long long iter = 0;
-            for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+            for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
                 const int acc = static_cast<int>(iter & 1);
                 const uint32_t acc_parity = static_cast<uint32_t>((iter >> 1) & 1);
                 bool ok = mbar_wait(smem_u32(bar_tempty + acc), acc_parity ^ 1u, abort_flag);
@@ -356,9 +384,9 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         const int row = q * 32 + lane;
         const int et = threadIdx.x - 64;
         long long iter = 0;
-        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
-            long long tm, tn;
-            decode_tile(tile, p.tiles_m, p.tiles_n, p.raster_group, &tm, &tn);
+        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+            uint32_t tm, tn;
+            decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &tm, &tn);
             const int acc = static_cast<int>(iter & 1);
             const uint32_t acc_parity = static_cast<uint32_t>((iter >> 1) & 1);
             // this thread's row of C
@@ -368,36 +396,95 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             long long row_off = slab_c_offset(p.a, tm * SA + a_slab, &digit0, &row_ok);
             row_ok = row_ok && (digit0 * p.a.slab_w + a_in < p.a.slab_mode_ext);
             row_off += a_in * p.a.row_elem_cstride;
-            // column table of this tile
-            long long* cols = col_off + acc * 256;
-            for (int j = et; j < p.BN; j += 128) {
-                bool col_ok;
-                int d0 = 0;
-                const int b_slab = j / p.b.slab_w, b_in = j % p.b.slab_w;
-                long long off = slab_c_offset(p.b, tn * SB + b_slab, &d0, &col_ok);
-                col_ok = col_ok && (d0 * p.b.slab_w + b_in < p.b.slab_mode_ext);
-                cols[j] = col_ok ? off + b_in * p.b.row_elem_cstride : -1;
+            // Column offsets of this tile.  A 32-column chunk of the accumulator never straddles a
+            // B slab when slabs are 32 or more columns wide, so one base offset and a valid-column
+            // count per chunk suffice (chunk table); narrower slabs use a per-column table.
+            const uint32_t cols = col_off + static_cast<uint32_t>(acc) * 256u * 8u;
+            const bool wide_slabs = p.b.slab_w >= 32;
+            if (wide_slabs) {
+                if (et < (p.BN >> 5)) {
+                    bool ch_ok;
+                    int d0 = 0;
+                    const int j = et * 32;
+                    const int b_slab = j / p.b.slab_w, b_in = j % p.b.slab_w;
+                    const long long off = slab_c_offset(p.b, tn * SB + b_slab, &d0, &ch_ok);
+                    int nvalid = p.b.slab_mode_ext - (d0 * p.b.slab_w + b_in);
+                    nvalid = !ch_ok ? 0 : nvalid > 32 ? 32 : nvalid < 0 ? 0 : nvalid;
+                    st_shared_s64(cols + static_cast<uint32_t>(et) * 16u, off + b_in * p.b.row_elem_cstride);
+                    st_shared_u32(cols + static_cast<uint32_t>(et) * 16u + 8u, static_cast<uint32_t>(nvalid));
+                }
+            } else {
+                for (int j = et; j < p.BN; j += 128) {
+                    bool col_ok;
+                    int d0 = 0;
+                    const int b_slab = j / p.b.slab_w, b_in = j % p.b.slab_w;
+                    long long off = slab_c_offset(p.b, tn * SB + b_slab, &d0, &col_ok);
+                    col_ok = col_ok && (d0 * p.b.slab_w + b_in < p.b.slab_mode_ext);
+                    st_shared_s64(cols + static_cast<uint32_t>(j) * 8u, col_ok ? off + b_in * p.b.row_elem_cstride : -1);
+                }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            const bool ok = mbar_wait(smem_u32(bar_tfull + acc), acc_parity, abort_flag);
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(smem_u32(bar_tfull + acc), acc_parity, abort_flag);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             tcgen05_fence_after();
             if (ok) {
                 float* crow = p.C + row_off;
-                for (int c0 = 0; c0 < p.BN; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * p.BN + c0), v);
-                    tmem_ld_wait();
-                    if (row_ok) {
+                const long long col_stride = p.b.row_elem_cstride;
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * p.BN);
+                const int nchunks = p.BN >> 5;
+                // TMEM loads run one chunk ahead of the stores.
+                auto store_chunk = [&](const uint32_t (&v)[32], int c) {
+                    if (wide_slabs) {
+                        const long long base = ld_shared_s64(cols + static_cast<uint32_t>(c) * 16u);
+                        const int nvalid = row_ok ? static_cast<int>(ld_shared_u32(cols + static_cast<uint32_t>(c) * 16u + 8u)) : 0;
+                        float* ptr = crow + base;
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
-                            const long long co = cols[c0 + j];
-                            if (co >= 0) __stcs(crow + co, __uint_as_float(v[j]));
+                            if (j < nvalid) __stcs(ptr, __uint_as_float(v[j]));
+                            ptr += col_stride;
                         }
+                    } else {
+                        // lane j keeps the offset of column 32*c + j; fetch all 32 by shuffle, then store
+                        const long long mine = ld_shared_s64(cols + static_cast<uint32_t>(c * 32 + lane) * 8u);
+                        const int lo = static_cast<int>(mine), hi = static_cast<int>(mine >> 32);
+                        long long co[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const unsigned ulo = static_cast<unsigned>(__shfl_sync(0xffffffffu, lo, j));
+                            const int shi = __shfl_sync(0xffffffffu, hi, j);
+                            co[j] = (static_cast<long long>(shi) << 32) | ulo;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (row_ok && co[j] >= 0) __stcs(crow + co[j], __uint_as_float(v[j]));
+                    }
+                };
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32(taddr, v0);
+                for (int c = 0; c < nchunks; c += 2) {
+                    tmem_ld_wait();
+                    if (c + 1 < nchunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 1) * 32), v1);
+                    else {
+                        // all of the accumulator is in registers: hand it back to the MMA warp early
+                        tcgen05_fence_before();
+                        mbar_arrive(smem_u32(bar_tempty + acc));
+                    }
+                    store_chunk(v0, c);
+                    if (c + 1 < nchunks) {
+                        tmem_ld_wait();
+                        if (c + 2 < nchunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 2) * 32), v0);
+                        else {
+                            tcgen05_fence_before();
+                            mbar_arrive(smem_u32(bar_tempty + acc));
+                        }
+                        store_chunk(v1, c + 1);
                     }
                 }
+            } else {
+                tcgen05_fence_before();
+                mbar_arrive(smem_u32(bar_tempty + acc));
             }
-            tcgen05_fence_before();
-            mbar_arrive(smem_u32(bar_tempty + acc));
         }
     }
 
@@ -407,7 +494,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
-    if (threadIdx.x == 0 && *abort_flag) atomicMax(p.status, 1);
+    if (threadIdx.x == 0 && ld_shared_u32(abort_flag)) atomicMax(p.status, 1);
 }
 
 }  // namespace
