@@ -141,6 +141,13 @@ tcontb_status tcontb_fill_uniform(void* dst, int scalar_type, int64_t n, uint64_
 tcontb_status tcontb_transpose(const void* src_dev, void* dst_dev, int rank, const int64_t* src_extent, const int* perm,
                                int elem_bytes, void* cuda_stream);
 
+/* Arithmetic-peak microbenchmarks on the current device, for roofline denominators (no
+ * counterpart in the reference): which = 0 TF32 tensor cores (tcgen05.mma kind::tf32 128x256x8
+ * issued back to back on resident operands), 1 = FP64 DFMA, 2 = FP64 mma.sync m8n8k4.
+ * Result in TFLOP/s, all SMs busy at once. */
+tcontb_status tcontb_measure_peak(int which, double* tflops);
+const char* tcontb_peak_last_error(void);
+
 /* ---- allocation-free contraction ------------------------------------------------------------
  *
  * No counterpart in the reference.  For callers that must not trigger a device allocation: a

@@ -317,3 +317,16 @@ def contract_no_alloc(desc: TCEquation, a_ptr: int, b_ptr: int, c_ptr: int, cuda
         if st == 3:
             raise NotImplementedError(msg)
         raise TcontError(msg)
+
+
+_lib.tcontb_measure_peak.argtypes = [C.c_int, C.POINTER(C.c_double)]
+_lib.tcontb_peak_last_error.restype = C.c_char_p
+
+
+def measure_peak(which: str) -> float:
+    """Arithmetic peak of the current device in TFLOP/s: 'tf32' (tcgen05), 'fp64_dfma', 'fp64_dmma'."""
+    v = C.c_double()
+    st = _lib.tcontb_measure_peak({"tf32": 0, "fp64_dfma": 1, "fp64_dmma": 2}[which], C.byref(v))
+    if st:
+        raise TcontError((_lib.tcontb_peak_last_error() or b"").decode())
+    return v.value

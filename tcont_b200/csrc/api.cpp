@@ -92,6 +92,7 @@ struct tcontb_run {
     UmmaParams umma{};
     CUtensorMap tmA{}, tmB{};
     DeviceBuffer status;
+    DeviceBuffer prof;  // cycle counters of the tcgen05 kernel, only with TCONT_UMMA_PROF=1
     // stage timing
     bool stage_timing = false;
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -100,6 +101,23 @@ struct tcontb_run {
 
     ~tcontb_run()
     {
+        if (prof.ptr) {
+            // Tuning aid: mean cycles per CTA spent in each role's waits during the last launch.
+            std::vector<long long> h(static_cast<size_t>(num_sms) * 8);
+            if (cudaMemcpy(h.data(), prof.ptr, h.size() * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess) {
+                double s[8] = {0};
+                int n = 0;
+                for (int b = 0; b < num_sms; ++b)
+                    if (h[static_cast<size_t>(b) * 8 + 4] > 0) {
+                        ++n;
+                        for (int i = 0; i < 8; ++i) s[i] += double(h[static_cast<size_t>(b) * 8 + i]);
+                    }
+                if (n)
+                    std::fprintf(stderr, "[tcontb prof] ctas=%d mma_total=%.0f mma_wait_acc_empty=%.0f mma_wait_stage_full=%.0f "
+                                 "producer_wait_stage_empty=%.0f epilogue_total=%.0f epilogue_wait_acc_full=%.0f (cycles, mean per CTA; MMA figures over issuing CTAs)\n",
+                                 n, s[0] / n, s[1] / n, s[2] / n, s[3] / n, s[4] / n, s[5] / n);
+            }
+        }
         for (auto& e : ev)
             if (e) cudaEventDestroy(e);
     }
@@ -116,6 +134,9 @@ void fill_operand_dev(const UmmaOperand& o, UmmaOperandDev* d)
     d->slabs_per_tile = o.slabs_per_tile;
     d->n_row_digits = o.n_row_digits;
     d->slab_bytes = o.slab_bytes;
+    d->slabs_per_op = o.slabs_per_op;
+    d->digit0_scale = o.digit0_scale;
+    d->oob_coord = o.oob_coord;
     for (int i = 0; i < kMaxTmaRank; ++i) {
         d->row_digit_dim[i] = i < o.n_row_digits ? o.row_digit_dim[i] : -1;
         d->row_digit_ext[i] = i < o.n_row_digits ? static_cast<int>(o.row_digit_ext[i]) : 1;
@@ -186,6 +207,7 @@ tcontb_status finish_run(tcontb_run* run)
         run->umma.BN = u.BN;
         run->umma.BK = u.BK;
         run->umma.stages = u.stages;
+        run->umma.pair = u.pair ? 1 : 0;
         run->umma.n_k_digits = u.n_k_digits;
         for (int i = 0; i < 3; ++i) run->umma.k_digit_ext[i] = static_cast<int>(u.k_digit_ext[i]);
         run->umma.k_iters = static_cast<int>(u.k_iters);
@@ -194,6 +216,14 @@ tcontb_status finish_run(tcontb_run* run)
         run->umma.raster_group = u.raster_group;
         run->umma.C = static_cast<float*>(run->dC);
         run->umma.status = static_cast<int*>(run->status.ptr);
+        run->umma.prof = nullptr;
+        if (const char* pe = std::getenv("TCONT_UMMA_PROF")) {
+            if (pe[0] == '1') {
+                TC_CUDA(run->prof.alloc(static_cast<size_t>(run->num_sms) * 8 * sizeof(long long)));
+                TC_CUDA(cudaMemset(run->prof.ptr, 0, static_cast<size_t>(run->num_sms) * 8 * sizeof(long long)));
+                run->umma.prof = static_cast<long long*>(run->prof.ptr);
+            }
+        }
         tcontb_status st = encode_map(u.a, kA, &run->tmA);
         if (st != TCONTB_OK) return st;
         st = encode_map(u.b, kB, &run->tmB);
@@ -228,6 +258,21 @@ tcontb_status finish_run(tcontb_run* run)
         run->simt.offCn = base + o[5];
         run->simt.a_along_k = pl.simt.a_load_along_k;
         run->simt.b_along_k = pl.simt.b_load_along_k;
+        if (pl.kernel == KERNEL_DMMA_F64) {
+            TC_CUDA(dmma_configure_all());
+            // 16-byte gathers: rows 2r and 2r+1 of the tile must be neighbours in memory, on a
+            // 16-byte boundary, for every contracted index.
+            auto pairs_ok = [](const std::vector<int64_t>& row, const std::vector<int64_t>& k) {
+                if (row.size() % 2) return false;
+                for (size_t r = 0; r < row.size(); r += 2)
+                    if ((row[r] & 1) || row[r + 1] != row[r] + 1) return false;
+                for (int64_t v : k)
+                    if (v & 1) return false;
+                return true;
+            };
+            if (run->simt.a_along_k == 0 && pairs_ok(t.offAm, t.offAk) && reinterpret_cast<uintptr_t>(kA) % 16 == 0) run->simt.a_along_k = 2;
+            if (run->simt.b_along_k == 0 && pairs_ok(t.offBn, t.offBk) && reinterpret_cast<uintptr_t>(kB) % 16 == 0) run->simt.b_along_k = 2;
+        }
     }
     const char* st_env = std::getenv("TCONT_STAGE_TIMES");
     run->stage_timing = st_env && std::strcmp(st_env, "1") == 0;
@@ -408,6 +453,8 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
     if (t) TC_CUDA(cudaEventRecord(run->ev[2], run->stream));
     if (pl.kernel == KERNEL_UMMA_TF32)
         TC_CUDA(launch_umma_tf32(run->umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
+    else if (pl.kernel == KERNEL_DMMA_F64)
+        TC_CUDA(launch_dmma_contract(run->simt, run->num_sms, run->stream));
     else
         TC_CUDA(launch_simt_contract(run->simt, pl.scalar_type, run->stream));
     if (t) {

@@ -21,12 +21,13 @@ struct SimtParams {
     const int64_t* offBk;
     const int64_t* offCm;
     const int64_t* offCn;
-    int a_along_k, b_along_k;
+    int a_along_k, b_along_k;  // 0: threads run along the rows, 1: along k, 2 (FP64 tensor kernel only): along the rows, two at a time
 };
 cudaError_t launch_simt_contract(const SimtParams& p, int scalar_type, cudaStream_t stream);
 
 // ---- FP64 tensor-core contraction (dmma_f64.cu), same GEMM view ----------------------------
-cudaError_t launch_dmma_contract(const SimtParams& p, cudaStream_t stream);
+cudaError_t launch_dmma_contract(const SimtParams& p, int num_sms, cudaStream_t stream);
+cudaError_t dmma_configure_all();  // once per device before the first launch
 
 // ---- tensor permutation (transpose.cu) ------------------------------------------------------
 struct TransposeParams {
@@ -43,6 +44,7 @@ cudaError_t launch_transpose(const void* src, void* dst, const TransposeParams& 
 // ---- TF32 tcgen05 contraction (umma_tf32.cu) -------------------------------------------------
 struct UmmaOperandDev {
     int major, slab_w, slabs_per_tile, n_row_digits, slab_bytes;
+    int slabs_per_op, digit0_scale, oob_coord;
     int row_digit_dim[kMaxTmaRank];
     int row_digit_ext[kMaxTmaRank];
     long long row_digit_cstride[kMaxTmaRank];
@@ -54,12 +56,14 @@ struct UmmaOperandDev {
 struct UmmaParams {
     UmmaOperandDev a, b;
     int BN, BK, stages, n_k_digits;
+    int pair;  // 1: two-CTA clusters, 256 x BN tiles (cta_group::2); 0: one CTA per 128 x BN tile
     int k_digit_ext[3];
     int k_iters;
     long long tiles_m, tiles_n;
     int raster_group;
     float* C;
     int* status;  // device status word: set non-zero when a bounded wait gives up
+    long long* prof;  // optional per-CTA cycle counters [grid][8] (TCONT_UMMA_PROF=1), else null
 };
 // tmapA / tmapB are 128-byte CUtensorMap objects passed by value as kernel parameters.
 cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,

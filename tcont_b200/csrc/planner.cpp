@@ -213,14 +213,14 @@ bool stage_operand(const Problem& p, const std::vector<int>& t, const std::vecto
 }
 
 void finish_operand(const Problem& p, const std::vector<int>& t, const std::vector<int>& rows, int tile_rows, int BK,
-                    const std::vector<int>& kdigits, UmmaOperand* o)
+                    const std::vector<int>& kdigits, UmmaOperand* o, int max_slab_rows = 256)
 {
     if (o->major == 0) {
         // K-major: rows per slab = the largest power of two (8..tile height) that pads the slab
         // mode by at most 15 %; failing that, the one that pads least.
         int best = 8;
         double best_waste = 1e30;
-        for (int w = 8; w <= tile_rows && w <= 256; w *= 2) {
+        for (int w = 8; w <= tile_rows && w <= max_slab_rows; w *= 2) {
             const double waste = double(ceil_div(o->slab_mode_ext, w) * w) / double(o->slab_mode_ext);
             const bool ok = waste <= 1.15, best_ok = best_waste <= 1.15;
             if ((ok && (!best_ok || w > best)) || (!ok && !best_ok && waste < best_waste - 1e-12)) {
@@ -259,6 +259,52 @@ void finish_operand(const Problem& p, const std::vector<int>& t, const std::vect
         o->box[o->slab_dim] = o->slab_w;
         o->slab_bytes = o->slab_w * 128;
     }
+    o->slabs_per_op = 1;
+    o->digit0_scale = o->slab_w;
+    o->oob_coord = static_cast<int>(ceil_div(o->slab_mode_ext, 32) * 32);
+}
+
+// Merged boxes for an MN-major operand: the slab mode (stride-1, extent a multiple of 32) is
+// presented to TMA as two dimensions (32 contiguous elements, extent/32 chunks), ordered
+// (lo, chunked K mode, hi, rest...), so that one copy with box {32, BK, g} lands g whole slabs one
+// after the other.  Fewer, larger copies: the 4 KB single-slab boxes kept the copy engine busy
+// with per-copy overhead (GEMM 8192x8192x4096 on B200: 377 TFLOP/s with 12 copies per stage
+// against 615 with 2).  `cta_slabs` = slabs of this operand one CTA stages per K step.
+void merge_slabs(UmmaOperand* o, int BK, int cta_slabs)
+{
+    if (o->major != 1 || o->rank > kMaxTmaRank - 1 || o->slab_dim != 0 || o->slab_mode_ext % 32) return;
+    const int64_t chunks = o->slab_mode_ext / 32;
+    int g = 1;
+    while (g * 2 <= cta_slabs && chunks % (g * 2) == 0 && cta_slabs % (g * 2) == 0) g *= 2;
+    if (g <= 1) return;
+    UmmaOperand n = *o;
+    int map[kMaxTmaRank];
+    for (int d = 0; d < kMaxTmaRank; ++d) map[d] = -1;
+    n.ext[0] = 32; n.stride[0] = 1;
+    n.ext[1] = o->ext[o->kc_dim]; n.stride[1] = o->stride[o->kc_dim];
+    n.ext[2] = chunks; n.stride[2] = 32;
+    map[0] = 2;
+    map[o->kc_dim] = 1;
+    int next = 3;
+    for (int d = 1; d < o->rank; ++d) {
+        if (d == o->kc_dim) continue;
+        n.ext[next] = o->ext[d];
+        n.stride[next] = o->stride[d];
+        map[d] = next++;
+    }
+    const int64_t total = o->stride[kMaxTmaRank - 1];  // padded dims carry the tensor's element count
+    for (int d = next; d < kMaxTmaRank; ++d) { n.ext[d] = 1; n.stride[d] = total; }
+    n.rank = o->rank + 1;
+    for (int d = 0; d < kMaxTmaRank; ++d) n.box[d] = 1;
+    n.box[0] = 32; n.box[1] = BK; n.box[2] = g;
+    n.slab_dim = 2;
+    n.kc_dim = 1;
+    for (int i = 0; i < o->n_row_digits; ++i) n.row_digit_dim[i] = map[o->row_digit_dim[i]];
+    for (int i = 0; i < 3; ++i) n.k_digit_dim[i] = o->k_digit_dim[i] >= 0 ? map[o->k_digit_dim[i]] : -1;
+    n.slabs_per_op = g;
+    n.digit0_scale = 1;
+    n.oob_coord = static_cast<int>(chunks);
+    *o = n;
 }
 
 void plan_umma(const Problem& p, UmmaSpec* u)
@@ -359,7 +405,40 @@ void plan_umma(const Problem& p, UmmaSpec* u)
         u->why_not = "tile or slab count does not fit 32 bits";
         return;
     }
-    const int stage_bytes = u->a.slabs_per_tile * u->a.slab_bytes + u->b.slabs_per_tile * u->b.slab_bytes;
+    // Two-CTA pairs (256-row tiles): each CTA stages its own 128 rows of A and half of the B tile,
+    // so B must split into an even number of slabs.  TCONT_UMMA_PAIR=1 selects it.
+    {
+        UmmaOperand b2 = u->b;
+        if (b2.major == 0 && b2.slabs_per_tile % 2) finish_operand(p, p.B, p.N, u->BN, BK, kdigits, &b2, u->BN / 2);
+        const int64_t tn2 = ceil_div(b2.total_slabs, b2.slabs_per_tile);
+        // (a short K loop is output-bound: pairing buys nothing there and costs the cluster handshakes)
+        // Measured on B200 the pair kernel does not beat one CTA per tile (GEMM 8192x8192x4096: 580 vs
+        // 605 TFLOP/s; cfg5: 455 vs 526): the MMA of a pair reads half of B from the partner SM and issues
+        // more slowly, which eats the saving in copies.  It therefore stays opt-in.
+        bool pair = false;
+        if (const char* e = std::getenv("TCONT_UMMA_PAIR")) {
+            if (e[0] == '0') pair = false;
+            else if (e[0] == '1') pair = u->tiles_m >= 2 && b2.slabs_per_tile % 2 == 0;
+        }
+        if (pair) {
+            u->pair = true;
+            u->b = b2;
+            u->tiles_n = tn2;
+        }
+    }
+    {
+        const double a_bytes = double(u->a.slabs_per_tile) * u->a.slab_bytes;
+        const double b_bytes = double(u->b.slabs_per_tile) * u->b.slab_bytes;
+        const bool a_far = u->a.major == 1 && u->a.stride[u->a.kc_dim] * 4 >= 65536;
+        const bool b_far = u->b.major == 1 && u->b.stride[u->b.kc_dim] * 4 >= 65536;
+        u->far_fraction = ((a_far ? a_bytes : 0.0) + (b_far ? b_bytes : 0.0)) / (a_bytes + b_bytes);
+    }
+    if (!std::getenv("TCONT_UMMA_NO_MERGE")) {
+        merge_slabs(&u->a, BK, u->a.slabs_per_tile);
+        merge_slabs(&u->b, BK, u->pair ? u->b.slabs_per_tile / 2 : u->b.slabs_per_tile);
+    }
+    const int stage_bytes = u->a.slabs_per_tile * u->a.slab_bytes +
+                            (u->pair ? u->b.slabs_per_tile / 2 : u->b.slabs_per_tile) * u->b.slab_bytes;
     const int budget = 227 * 1024 - 8 * 1024;
     u->stages = std::max(2, std::min(8, budget / stage_bytes));
     u->smem_bytes = u->stages * stage_bytes + 8 * 1024 + 1024;
@@ -388,14 +467,26 @@ void fill_transpose(const std::string& src, const std::string& dst, const std::s
     }
 }
 
+// FP64 goes to the tensor-path kernel (128 x 128 tiles) once there is a tile per SM; smaller
+// problems keep the 64 x 64 CUDA-core tiles, which spread over more SMs.
+int pick_kernel(const Problem& p, const UmmaSpec& u)
+{
+    if (u.eligible) return KERNEL_UMMA_TF32;
+    const char* k = std::getenv("TCONT_KERNEL");
+    const bool simt_only = k && std::strcmp(k, "simt") == 0;
+    if (p.scalar_type == 1 && !simt_only && ceil_div(p.Mtot, 128) * ceil_div(p.Ntot, 128) >= 148) return KERNEL_DMMA_F64;
+    return KERNEL_SIMT;
+}
+
 double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const CostTable& c)
 {
     const double elt = p.scalar_type == 1 ? 8.0 : 4.0;
     const double flops = 2.0 * double(p.Mtot) * double(p.Ntot) * double(p.Ktot);
     double c_bytes = double(p.sizeC) * elt;
     double rate = p.scalar_type == 1 ? c.simt_f64_tflops : c.simt_f32_tflops;
+    if (kernel == KERNEL_DMMA_F64) rate = c.dmma_f64_tflops;
     if (kernel == KERNEL_UMMA_TF32) {
-        rate = c.umma_tf32_tflops;
+        rate = c.umma_tf32_tflops * (1.0 - c.far_row_penalty * u.far_fraction);
         // rows of a slab that are not contiguous in C cost a 32-byte sector per element
         if (u.a.row_elem_cstride != 1) c_bytes *= 8.0;
     }
@@ -420,6 +511,8 @@ CostTable load_cost_table()
         else if (key == "simt_f32_tflops") c.simt_f32_tflops = v;
         else if (key == "simt_f64_tflops") c.simt_f64_tflops = v;
         else if (key == "launch_us") c.launch_us = v;
+        else if (key == "dmma_f64_tflops") c.dmma_f64_tflops = v;
+        else if (key == "far_row_penalty") c.far_row_penalty = v;
     }
     return c;
 }
@@ -478,24 +571,74 @@ int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* 
 
     UmmaSpec direct_umma;
     plan_umma(direct, &direct_umma);
-    const int direct_kernel = direct_umma.eligible ? KERNEL_UMMA_TF32 : KERNEL_SIMT;
+    const int direct_kernel = pick_kernel(direct, direct_umma);
     pl.est_direct_us = contraction_us(direct, direct_kernel, direct_umma, cost);
 
-    // Transpose-assisted candidate: role A becomes [M modes in C order | K modes], role B becomes
-    // [N modes in C order | K modes]; C is written in its final order by the contraction kernel,
-    // so there is no third transpose (the reference's TTGT always pays C' -> C,
+    // Transpose-assisted candidate.  A role's transposed layout is
+    //     [lead | K modes | remaining row modes in C order]
+    // where `lead` is the shortest run of the role's first row modes (consecutive in C) whose fused
+    // extent is a multiple of 32: the slab mode stays stride-1 and the K rows of a tile follow it
+    // directly, so a TMA box is one contiguous piece of memory.  An operand that already starts
+    // with [lead, first K mode] (or is K-major on that K mode) is used where it lies.  Three K
+    // orders are tried (by A's strides, by B's strides, the direct plan's); the one that moves
+    // the fewest bytes wins.  C is written in its final order by the contraction kernel, so
+    // there is never a third transpose (the reference's TTGT always pays C' -> C,
     // backends/ttgt_cutt/src/ttgt_cutt.cpp:811-816).
     const std::string& roleA_src = direct.swapped ? pl.modeB : pl.modeA;
     const std::string& roleB_src = direct.swapped ? pl.modeA : pl.modeB;
-    const std::string kmodes = perm_modes(direct, direct.K);
-    const std::string roleA_dst = perm_modes(direct, direct.M) + kmodes;
-    const std::string roleB_dst = perm_modes(direct, direct.N) + kmodes;
+    auto ext_of = [&](char c) { return pl.ext_val[static_cast<size_t>(find_char(pl.ext_mode, c))]; };
+    auto lead_of = [&](const std::string& src) {  // row modes of `src` in C order, split into (lead, rest)
+        std::string rows;
+        for (char c : pl.modeC)
+            if (find_char(src, c) >= 0) rows.push_back(c);
+        size_t n = 0;
+        int64_t prod = 1;
+        bool found = false;
+        while (n < rows.size()) {
+            if (n > 0 && find_char(pl.modeC, rows[n]) != find_char(pl.modeC, rows[n - 1]) + 1) break;
+            prod *= ext_of(rows[n]);
+            ++n;
+            if (prod % 32 == 0) { found = true; break; }
+        }
+        if (!found) {  // no multiple of 32: keep the whole leading run together
+            n = 1;
+            while (n < rows.size() && find_char(pl.modeC, rows[n]) == find_char(pl.modeC, rows[n - 1]) + 1) ++n;
+        }
+        return std::make_pair(rows.substr(0, n), rows.substr(n));
+    };
+    const auto leadA = lead_of(roleA_src), leadB = lead_of(roleB_src);
+    std::string kall;
+    for (char c : roleA_src)
+        if (find_char(pl.modeC, c) < 0) kall.push_back(c);
+    auto sorted_by = [&](const std::string& src) {
+        std::string k = kall;
+        std::sort(k.begin(), k.end(), [&](char x, char y) { return find_char(src, x) < find_char(src, y); });
+        return k;
+    };
+    auto starts_with = [](const std::string& s, const std::string& pre) { return s.compare(0, pre.size(), pre) == 0; };
+    std::string roleA_dst = roleA_src, roleB_dst = roleB_src;
+    {
+        double best = 1e300;
+        for (const std::string& korder : {sorted_by(roleB_src), sorted_by(roleA_src), perm_modes(direct, direct.K)}) {
+            if (korder.empty()) continue;
+            auto keep = [&](const std::string& src, const std::string& lead) {
+                return src[0] == korder[0] || starts_with(src, lead + korder[0]);
+            };
+            const bool keepA = keep(roleA_src, leadA.first), keepB = keep(roleB_src, leadB.first);
+            const double moved = (keepA ? 0.0 : double(direct.sizeA)) + (keepB ? 0.0 : double(direct.sizeB));
+            if (moved < best) {
+                best = moved;
+                roleA_dst = keepA ? roleA_src : leadA.first + korder + leadA.second;
+                roleB_dst = keepB ? roleB_src : leadB.first + korder + leadB.second;
+            }
+        }
+    }
     Problem ttgt;
     rc = build_problem(pl.modeC, roleA_dst, roleB_dst, pl.ext_mode, pl.ext_val, scalar_type, &ttgt, err);
     if (rc) return rc;
     UmmaSpec ttgt_umma;
     plan_umma(ttgt, &ttgt_umma);
-    const int ttgt_kernel = ttgt_umma.eligible ? KERNEL_UMMA_TF32 : KERNEL_SIMT;
+    const int ttgt_kernel = pick_kernel(ttgt, ttgt_umma);
     TransposeSpec tA, tB;
     fill_transpose(roleA_src, roleA_dst, pl.ext_mode, pl.ext_val, &tA);
     fill_transpose(roleB_src, roleB_dst, pl.ext_mode, pl.ext_val, &tB);
@@ -590,9 +733,9 @@ std::string describe_plan(const Plan& pl)
     if (!u.eligible) o << ",\"why_not\":\"" << u.why_not << "\"";
     else {
         o << ",\"BM\":" << u.BM << ",\"BN\":" << u.BN << ",\"BK\":" << u.BK << ",\"stages\":" << u.stages
-          << ",\"kc\":\"" << u.kc_names << "\",\"k_iters\":" << u.k_iters << ",\"tiles_m\":" << u.tiles_m << ",\"tiles_n\":" << u.tiles_n
+          << ",\"pair\":" << (u.pair ? "true" : "false") << ",\"kc\":\"" << u.kc_names << "\",\"k_iters\":" << u.k_iters << ",\"tiles_m\":" << u.tiles_m << ",\"tiles_n\":" << u.tiles_n
           << ",\"a_major\":\"" << (u.a.major ? "MN" : "K") << "\",\"b_major\":\"" << (u.b.major ? "MN" : "K") << "\""
-          << ",\"a_slab_w\":" << u.a.slab_w << ",\"b_slab_w\":" << u.b.slab_w << ",\"a_slabs\":" << u.a.slabs_per_tile
+          << ",\"a_slab_w\":" << u.a.slab_w << ",\"b_slab_w\":" << u.b.slab_w << ",\"a_slabs_per_copy\":" << u.a.slabs_per_op << ",\"b_slabs_per_copy\":" << u.b.slabs_per_op << ",\"a_slabs\":" << u.a.slabs_per_tile
           << ",\"b_slabs\":" << u.b.slabs_per_tile << ",\"smem_bytes\":" << u.smem_bytes
           << ",\"coalesced_store\":" << (u.a.row_elem_cstride == 1 ? "true" : "false");
     }

@@ -60,6 +60,9 @@ struct UmmaOperand {
     int slab_dim = 0;      // tensor dim the slab runs along
     int kc_dim = 0;        // tensor dim of the chunked K mode
     int slabs_per_tile = 4;
+    int slabs_per_op = 1;    // consecutive slabs fetched by one TMA copy (merged boxes, MN-major only)
+    int digit0_scale = 32;   // TMA coordinate of row digit 0 = chunk index * this
+    int oob_coord = 0;       // coordinate (in row digit 0's dim) that lies past the tensor: zero fill
     int n_row_digits = 1;  // slab index = mixed radix number; digit 0 = chunk of the slab mode
     int row_digit_dim[kMaxTmaRank] = {0};
     int64_t row_digit_ext[kMaxTmaRank] = {1};
@@ -80,7 +83,9 @@ struct UmmaSpec {
     int n_k_digits = 1;
     int64_t k_digit_ext[3] = {1, 1, 1};  // digit 0 = chunks of the chunked K mode
     int64_t k_iters = 1, tiles_m = 1, tiles_n = 1;
+    double far_fraction = 0;  // share of a stage's bytes whose K rows are 64 KB or more apart in memory
     int raster_group = 16;
+    bool pair = false;  // two-CTA clusters working on 256-row tiles (tcgen05 cta_group::2)
     int smem_bytes = 0;
 };
 
@@ -95,8 +100,12 @@ struct CostTable {
     double hbm_gbs = 6546.9;
     double umma_tf32_tflops = 600.0;
     double simt_f32_tflops = 20.0;
-    double simt_f64_tflops = 15.0;
+    double simt_f64_tflops = 14.0;
+    double dmma_f64_tflops = 28.0;
     double launch_us = 3.0;
+    // Fraction of the tcgen05 rate lost per unit of staged bytes whose K rows lie 64 KB or more apart
+    // (cfg5 on B200: 274 / 434 / 605 TFLOP/s with two thirds / one third / none of the bytes far-strided).
+    double far_row_penalty = 0.85;
 };
 
 struct Plan {

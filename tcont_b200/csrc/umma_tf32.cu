@@ -114,6 +114,58 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* tmap, uint
         : "memory");
 }
 
+// The same copy for a CTA pair: the destination is this CTA's shared memory, the mbarrier may live
+// in the partner CTA (address in the cluster window).  No multicast.
+__device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0, int c1, int c2, int c3, int c4)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+// One commit that arrives on the barrier at the same offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(static_cast<unsigned short>(3)) : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -197,6 +249,13 @@ __device__ __forceinline__ long long slab_c_offset(const UmmaOperandDev& o, uint
     return off;
 }
 
+// PAIR = false: one CTA per 128 x BN tile (cta_group::1).
+// PAIR = true : a cluster of two CTAs per 256 x BN tile (cta_group::2).  CTA r of the pair stages its own
+//               128 rows of A and half of the B tile (no multicast; every copy is a plain TMA load into
+//               the issuing CTA), CTA 0 issues the MMAs for both, each CTA drains its own 128 x BN
+//               accumulator.  B traffic per flop halves, which is what the operand-fetch-bound 1-CTA
+//               kernel lacks.
+template <bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                  const __grid_constant__ UmmaParams p)
@@ -204,9 +263,11 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // 1024-byte aligned
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;        // 0 = the CTA that issues the MMAs
     const int SA = p.a.slabs_per_tile, SB = p.b.slabs_per_tile;
+    const int SBL = PAIR ? SB / 2 : SB;                       // B slabs this CTA stages itself
     const uint32_t a_tile_bytes = static_cast<uint32_t>(SA * p.a.slab_bytes);
-    const uint32_t stage_bytes = a_tile_bytes + static_cast<uint32_t>(SB * p.b.slab_bytes);
+    const uint32_t stage_bytes = a_tile_bytes + static_cast<uint32_t>(SBL * p.b.slab_bytes);
 
     uint8_t* aux = smem + static_cast<size_t>(p.stages) * stage_bytes;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(aux);  // [8]
@@ -227,32 +288,45 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(bar_tfull + a), 1);
-            mbar_init(smem_u32(bar_tempty + a), 128);
+            mbar_init(smem_u32(bar_tempty + a), PAIR ? 256 : 128);
         }
         st_shared_u32(abort_flag, 0u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // the partner's barriers exist before anything signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t tiles_m = static_cast<uint32_t>(p.tiles_m), tiles_n = static_cast<uint32_t>(p.tiles_n);
+    // Work units: 128-row tiles, or 256-row tile pairs; unit u of a pair covers row tiles 2u and 2u+1.
+    const uint32_t tiles_m = PAIR ? (static_cast<uint32_t>(p.tiles_m) + 1u) / 2u : static_cast<uint32_t>(p.tiles_m);
+    const uint32_t tiles_n = static_cast<uint32_t>(p.tiles_n);
     const uint32_t total_tiles = tiles_m * tiles_n;
+    const uint32_t first_unit = PAIR ? blockIdx.x / 2u : blockIdx.x;
+    const uint32_t unit_step = PAIR ? gridDim.x / 2u : gridDim.x;
 
     if (warp == 0) {
         // ---------------- TMA producer: lane i owns slab i of the stage ----------------
-        const bool is_a = lane < SA;
-        const bool active = lane < SA + SB;
+        // lane i owns copy i of the stage; a copy brings slabs_per_op consecutive slabs
+        const int OA = SA / p.a.slabs_per_op, OBL = SBL / p.b.slabs_per_op;
+        const bool is_a = lane < OA;
+        const bool active = lane < OA + OBL;
         const UmmaOperandDev& o = is_a ? p.a : p.b;
         const void* tmap = is_a ? static_cast<const void*>(&tmapA) : static_cast<const void*>(&tmapB);
-        const int slab = is_a ? lane : lane - SA;
+        const int slab = is_a ? lane * p.a.slabs_per_op : (lane - OA) * p.b.slabs_per_op;   // first slab of the copy, inside this CTA's part
         const uint32_t my_off = is_a ? static_cast<uint32_t>(slab * p.a.slab_bytes)
                                      : a_tile_bytes + static_cast<uint32_t>(slab * p.b.slab_bytes);
         if (lane == 0) {
@@ -262,12 +336,15 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         int stage = 0;
         uint32_t phase = 0;
         uint32_t issued_mask = 0, issued_parity = 0;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        long long t_empty = 0;
+
+        for (uint32_t tile = first_unit; tile < total_tiles; tile += unit_step) {
             uint32_t tm, tn;
             decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &tm, &tn);
             int base[kMaxTmaRank] = {0, 0, 0, 0, 0};
             if (active) {
-                const uint32_t s = (is_a ? tm * SA : tn * SB) + slab;
+                const uint32_t s = is_a ? (PAIR ? 2u * tm + rank : tm) * SA + slab
+                                        : tn * SB + (PAIR ? rank * SBL : 0u) + slab;
                 if (s < static_cast<uint32_t>(o.total_slabs)) {
                     uint32_t rem = s;
 #pragma unroll
@@ -276,7 +353,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                             const uint32_t e = static_cast<uint32_t>(o.row_digit_ext[d]);
                             const int idx = static_cast<int>(rem % e);
                             rem /= e;
-                            const int v = d == 0 ? idx * o.slab_w : idx;
+                            const int v = d == 0 ? idx * o.digit0_scale : idx;
 #pragma unroll
                             for (int t = 0; t < kMaxTmaRank; ++t)
                                 if (o.row_digit_dim[d] == t) base[t] = v;
@@ -286,14 +363,18 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                     // Slab beyond the tensor: start the box past the slab mode's end, TMA fills zeros.
 #pragma unroll
                     for (int t = 0; t < kMaxTmaRank; ++t)
-                        if (o.row_digit_dim[0] == t) base[t] = ((o.slab_mode_ext + 31) / 32) * 32;
+                        if (o.row_digit_dim[0] == t) base[t] = o.oob_coord;
                 }
             }
             int kd0 = 0, kd1 = 0, kd2 = 0;  // K digits: chunk of the chunked mode, then the other K modes
             for (int it = 0; it < p.k_iters; ++it) {
+                const long long t0 = p.prof ? clock64() : 0;
                 const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + stage), phase ^ 1u, abort_flag));
+                if (p.prof) t_empty += clock64() - t0;
                 if (ok) {
-                    if (lane == 0) mbar_arrive_expect_tx(smem_u32(bar_full + stage), stage_bytes);
+                    // one arrival with the byte count of the whole stage; in a pair the MMA-issuing CTA
+                    // accounts for both CTAs' copies, which all signal its barrier
+                    if (lane == 0 && rank == 0) mbar_arrive_expect_tx(smem_u32(bar_full + stage), PAIR ? 2u * stage_bytes : stage_bytes);
                     __syncwarp();
                     if (active) {
                         int c[kMaxTmaRank];
@@ -304,8 +385,9 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                             if (o.k_digit_dim[1] == t) c[t] = kd1;
                             if (o.k_digit_dim[2] == t) c[t] = kd2;
                         }
-                        tma_load_5d(smem_u32(smem + static_cast<size_t>(stage) * stage_bytes + my_off), tmap,
-                                    smem_u32(bar_full + stage), c[0], c[1], c[2], c[3], c[4]);
+                        const uint32_t dst = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes + my_off);
+                        if (PAIR) tma_load_5d_pair(dst, tmap, map_to_cta(smem_u32(bar_full + stage), 0u), c[0], c[1], c[2], c[3], c[4]);
+                        else tma_load_5d(dst, tmap, smem_u32(bar_full + stage), c[0], c[1], c[2], c[3], c[4]);
                     }
                     issued_mask |= 1u << stage;
                     issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
@@ -323,8 +405,9 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                 }
             }
         }
-        if (ld_shared_u32(abort_flag) && lane == 0) {
-            // Give the bulk copies this warp issued a bounded time to land before the CTA ends.
+        if (p.prof && lane == 0) p.prof[blockIdx.x * 8 + 3] = t_empty;
+        if (ld_shared_u32(abort_flag) && lane == 0 && rank == 0) {
+            // Give the bulk copies issued into this barrier a bounded time to land before the CTA ends.
             for (int s = 0; s < p.stages; ++s) {
                 if (!(issued_mask & (1u << s))) continue;
                 const unsigned long long t0 = global_timer();
@@ -334,10 +417,10 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(p.a.major) << 15) |
                                    (static_cast<uint32_t>(p.b.major) << 16) | (static_cast<uint32_t>(p.BN >> 3) << 17) |
-                                   (static_cast<uint32_t>(128 >> 4) << 24);
+                                   (static_cast<uint32_t>((PAIR ? 256 : 128) >> 4) << 24);
             // MN-major: slabs sit one leading-byte-offset apart; the 8 K rows of one MMA are two
             //           4-row groups 512 bytes apart (stride byte offset), 1024 bytes per MMA.
             // K-major : 8-row groups sit 1024 bytes apart, 8 K elements per MMA = 32 bytes.
@@ -351,14 +434,19 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             int stage = 0;
             uint32_t phase = 0;
             long long iter = 0;
-            for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+            long long t_tempty = 0, t_full = 0, t_all = clock64();
+            for (uint32_t tile = first_unit; tile < total_tiles; tile += unit_step, ++iter) {
                 const int acc = static_cast<int>(iter & 1);
                 const uint32_t acc_parity = static_cast<uint32_t>((iter >> 1) & 1);
+                long long t0 = p.prof ? clock64() : 0;
                 bool ok = mbar_wait(smem_u32(bar_tempty + acc), acc_parity ^ 1u, abort_flag);
+                if (p.prof) t_tempty += clock64() - t0;
                 tcgen05_fence_after();
                 const uint32_t tmem_c = tmem_base + static_cast<uint32_t>(acc * p.BN);
                 for (int it = 0; it < p.k_iters; ++it) {
+                    t0 = p.prof ? clock64() : 0;
                     ok = ok && mbar_wait(smem_u32(bar_full + stage), phase, abort_flag);
+                    if (p.prof) t_full += clock64() - t0;
                     if (ok) {
                         tcgen05_fence_after();
                         const uint32_t a_base = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
@@ -366,16 +454,33 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                         for (int kk = 0; kk < ksteps; ++kk) {
                             const uint64_t da = smem_desc(a_base + kk * a_kstep, a_lbo, a_sbo, a_type);
                             const uint64_t db = smem_desc(b_base + kk * b_kstep, b_lbo, b_sbo, b_type);
-                            umma_tf32(tmem_c, da, db, idesc, (it | kk) != 0 ? 1u : 0u);
+                            if (PAIR) umma_tf32_pair(tmem_c, da, db, idesc, (it | kk) != 0 ? 1u : 0u);
+                            else umma_tf32(tmem_c, da, db, idesc, (it | kk) != 0 ? 1u : 0u);
                         }
-                        umma_commit(smem_u32(bar_empty + stage));  // frees the stage once the MMAs have read it
+                        // frees the stage (in both CTAs of a pair) once the MMAs have read it
+                        if (PAIR) {
+                            umma_commit_pair_both(smem_u32(bar_empty + stage));
+                        } else {
+                            umma_commit(smem_u32(bar_empty + stage));
+                        }
                     }
                     if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-                if (ok) umma_commit(smem_u32(bar_tfull + acc));  // accumulator complete
+                if (ok) {  // accumulator complete
+                    if (PAIR) {
+                        umma_commit_pair_both(smem_u32(bar_tfull + acc));
+                    } else {
+                        umma_commit(smem_u32(bar_tfull + acc));
+                    }
+                }
+            }
+            if (p.prof) {
+                p.prof[blockIdx.x * 8 + 0] = clock64() - t_all;
+                p.prof[blockIdx.x * 8 + 1] = t_tempty;
+                p.prof[blockIdx.x * 8 + 2] = t_full;
             }
         }
     } else {
@@ -384,7 +489,8 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         const int row = q * 32 + lane;
         const int et = threadIdx.x - 64;
         long long iter = 0;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+        long long t_tfull = 0, t_epi = clock64();
+        for (uint32_t tile = first_unit; tile < total_tiles; tile += unit_step, ++iter) {
             uint32_t tm, tn;
             decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &tm, &tn);
             const int acc = static_cast<int>(iter & 1);
@@ -393,7 +499,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             bool row_ok;
             int digit0 = 0;
             const int a_slab = row / p.a.slab_w, a_in = row % p.a.slab_w;
-            long long row_off = slab_c_offset(p.a, tm * SA + a_slab, &digit0, &row_ok);
+            long long row_off = slab_c_offset(p.a, (PAIR ? 2u * tm + rank : tm) * SA + a_slab, &digit0, &row_ok);
             row_ok = row_ok && (digit0 * p.a.slab_w + a_in < p.a.slab_mode_ext);
             row_off += a_in * p.a.row_elem_cstride;
             // Column offsets of this tile.  A 32-column chunk of the accumulator never straddles a
@@ -424,8 +530,16 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                 }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            // accumulator-empty barrier lives in the MMA-issuing CTA; in a pair both CTAs' epilogues arrive on it
+            const uint32_t tempty_addr = PAIR ? map_to_cta(smem_u32(bar_tempty + acc), 0u) : smem_u32(bar_tempty + acc);
+            auto release_acc = [&]() {
+                if (PAIR) mbar_arrive_cluster(tempty_addr);
+                else mbar_arrive(tempty_addr);
+            };
             bool ok = true;
+            const long long t0 = p.prof ? clock64() : 0;
             if (lane == 0) ok = mbar_wait(smem_u32(bar_tfull + acc), acc_parity, abort_flag);
+            if (p.prof) t_tfull += clock64() - t0;
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             tcgen05_fence_after();
             if (ok) {
@@ -468,7 +582,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                     else {
                         // all of the accumulator is in registers: hand it back to the MMA warp early
                         tcgen05_fence_before();
-                        mbar_arrive(smem_u32(bar_tempty + acc));
+                        release_acc();
                     }
                     store_chunk(v0, c);
                     if (c + 1 < nchunks) {
@@ -476,23 +590,29 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                         if (c + 2 < nchunks) tmem_ld_32x32(taddr + static_cast<uint32_t>((c + 2) * 32), v0);
                         else {
                             tcgen05_fence_before();
-                            mbar_arrive(smem_u32(bar_tempty + acc));
+                            release_acc();
                         }
                         store_chunk(v1, c + 1);
                     }
                 }
             } else {
                 tcgen05_fence_before();
-                mbar_arrive(smem_u32(bar_tempty + acc));
+                release_acc();
             }
+        }
+        if (p.prof && et == 0) {
+            p.prof[blockIdx.x * 8 + 4] = clock64() - t_epi;
+            p.prof[blockIdx.x * 8 + 5] = t_tfull;
         }
     }
 
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // neither CTA leaves while its partner may still read or signal its memory
     tcgen05_fence_after();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
     if (threadIdx.x == 0 && ld_shared_u32(abort_flag)) atomicMax(p.status, 1);
 }
@@ -501,17 +621,38 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
 
 cudaError_t umma_tf32_configure(int smem_bytes)
 {
-    return cudaFuncSetAttribute(umma_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    cudaError_t e = cudaFuncSetAttribute(umma_tf32_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(umma_tf32_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
 }
 
 cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,
                              cudaStream_t stream)
 {
+    const CUtensorMap& ta = *static_cast<const CUtensorMap*>(tmapA);
+    const CUtensorMap& tb = *static_cast<const CUtensorMap*>(tmapB);
+    if (p.pair) {
+        const long long units = ((p.tiles_m + 1) / 2) * p.tiles_n;
+        if (units <= 0) return cudaErrorInvalidValue;
+        const long long clusters = units < num_sms / 2 ? units : num_sms / 2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, umma_tf32_kernel<true>, ta, tb, p);
+    }
     const long long total = p.tiles_m * p.tiles_n;
     if (total <= 0) return cudaErrorInvalidValue;
     const unsigned grid = static_cast<unsigned>(total < num_sms ? total : num_sms);
-    umma_tf32_kernel<<<grid, kThreads, smem_bytes, stream>>>(*static_cast<const CUtensorMap*>(tmapA),
-                                                            *static_cast<const CUtensorMap*>(tmapB), p);
+    umma_tf32_kernel<false><<<grid, kThreads, smem_bytes, stream>>>(ta, tb, p);
     return cudaGetLastError();
 }
 

@@ -89,6 +89,18 @@ def test_tensor_core_shapes(engine, oracle, name):
     check(oracle, c, A, B, out, desc)
 
 
+@pytest.mark.parametrize("c", [
+    Contraction("abcd", "aebf", "fdec", dict(a=50, b=30, c=34, d=50, e=13, f=3), F64),      # ragged in M, N and K
+    Contraction("abcijk", "aeij", "bcek", dict(a=48, b=12, c=12, e=48, i=6, j=6, k=12), F64),  # cfg3's pattern
+    Contraction("ab", "ka", "kb", dict(a=1537, b=1409, k=70), F64),                          # both K-major
+], ids=["ragged4d", "cfg3_like", "kmajor"])
+def test_fp64_tensor_path(engine, oracle, c):
+    A, B = oracle.inputs(c, 31, -1.0, 1.0)
+    out, desc = run_contraction(engine, c, A, B, 1)
+    assert desc["kernel"] == "dmma_f64"
+    check(oracle, c, A, B, out, desc)
+
+
 def test_tf32_operands_are_truncated_not_rounded(engine, oracle):
     """Pins how the tensor core narrows raw fp32 operands (the reference hands WMMA raw bits too,
     kernel_compute.py:851+): values with all 13 low mantissa bits set, K = 8."""

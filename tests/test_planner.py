@@ -34,9 +34,10 @@ def test_backend_selection_and_names(engine):
     p = engine.plan(to_equation(engine, c, 2))
     assert p.backend == engine.Backend.TTGT_CUTT
     d = p.describe()
-    # role A = A[a,e,b,f] -> [a,b | K], role B = B[f,d,e,c] -> [c,d | K]; C needs no transpose
-    assert d["transpose_a"] == [0, 2, 3, 1] and d["transpose_b"] == [3, 1, 0, 2]
-    assert d["A"] == ["ab:576", "fe:256"] and d["B"] == ["cd:576", "fe:256"]
+    # role A = A[a,e,b,f] -> [a,b | f,e] (lead = ab, K in B's order); B[f,d,e,c] is K-major on f and
+    # is used where it lies; C never needs a transpose
+    assert d["transpose_a"] == [0, 2, 3, 1] and d["transpose_b"] is None
+    assert d["A"] == ["ab:576", "f:16", "e:16"] and d["B"] == ["f:16", "d:24", "e:16", "c:24"]
 
 
 def test_configs_pick_the_intended_kernels(engine):
@@ -47,10 +48,14 @@ def test_configs_pick_the_intended_kernels(engine):
     assert u["tiles_m"] * u["tiles_n"] == 2048 and u["coalesced_store"] and u["smem_bytes"] <= 227 * 1024
     d4 = describe(engine, CONFIGS["cfg4"][0])
     assert d4["backend"] == "ttgt" and d4["kernel"] == "umma_tf32" and d4["umma"]["BK"] == 8
-    assert d4["transpose_a"] == [3, 2, 0, 1] and d4["A"] == ["ab:2304", "e:48", "f:8"]
+    assert d4["transpose_a"] == [3, 2, 1, 0] and d4["A"] == ["ab:2304", "f:8", "e:48"] and d4["umma"]["pair"] is False
+    # cfg5: A's contracted rows lie 8 MB apart; the cost table sends A through one transpose to
+    # [a | f,e | b] so that every TMA box is one contiguous piece, and keeps B where it lies
     d5 = describe(engine, CONFIGS["cfg5"][0])
-    assert d5["kernel"] == "umma_tf32" and d5["umma"]["k_iters"] == 512
-    assert describe(engine, CONFIGS["cfg3"][0])["kernel"] == "simt"
+    assert d5["backend"] == "ttgt" and d5["transpose_a"] == [0, 3, 1, 2] and d5["transpose_b"] is None
+    assert d5["kernel"] == "umma_tf32" and d5["umma"]["k_iters"] == 512 and d5["umma"]["kc"] == "f"
+    assert d2["umma"]["pair"] is False and d2["umma"]["a_slabs_per_copy"] == 4
+    assert describe(engine, CONFIGS["cfg3"][0])["kernel"] == "dmma_f64"   # a 128x128 tile per SM and more
     assert describe(engine, CONFIGS["cfg1"][0])["kernel"] == "simt"
 
 
