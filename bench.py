@@ -32,10 +32,13 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     "cfg1": ("abcd", "aebf", "fdec", dict(a=24, b=24, c=24, d=24, e=16, f=16), 1, 0, -1.0, 1.0, "d", "tensor", "d", 24),
     "cfg2": ("abc", "adc", "db", dict(a=256, c=256, b=1024, d=1024), 0, 1, -1.0, 1.0, "c", "tensor", "c", 32),
-    "cfg3": ("abcijk", "aeij", "bcek", dict(a=48, b=48, c=48, e=48, i=24, j=24, k=24), 1, 2, -0.5, 0.5, "k", "hbm", "k", 1),
+    "cfg3": ("abcijk", "aeij", "bcek", dict(a=48, b=48, c=48, e=48, i=24, j=24, k=24), 1, 2, -0.5, 0.5, "k", "tensor", "k", 1),
     "cfg4": ("abcde", "efba", "cfd", dict(a=48, b=48, c=48, d=48, e=48, f=8), 0, 3, -1.0, 1.0, "d", "hbm", "d", 24),
     "cfg5": ("abcd", "aebf", "cfde", dict(a=128, b=128, c=128, d=128, e=128, f=128), 0, 4, -1.0, 1.0, "d", "tensor", "d", 1),
 }
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
+# captures summarised under profiles/; None where no capture of that workload exists.
+NCU_TRAFFIC = {"cfg2": 498.7e6}
 REF_CASE = {"cfg1": 21, "cfg2": 18}   # reference loop nests with the same mode pattern (tccg_verify.cpp:660-689, :567-592)
 
 
@@ -172,6 +175,13 @@ def main():
     ap.add_argument("--backend", default="model", choices=["model", "cogent", "ttgt"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: the global problem grows with N (default); strong: the named configuration is cut into N slices")
+    ap.add_argument("--split", default="external", choices=["external", "contracted"],
+                    help="contracted: cut a contracted mode; every rank produces a full-size partial C and an NCCL "
+                         "reduce-scatter over NVLink adds them (strong scaling only)")
+    ap.add_argument("--split-mode", default=None, help="mode letter to cut (default: the workload's slowest external mode; "
+                                                       "for --split contracted the first contracted mode of A)")
     args = ap.parse_args()
     name = args.workload
     if args.impl == "reference":
@@ -195,18 +205,41 @@ def main():
 
     mC, mA, mB, ext, st, seed, lo, hi, shard_mode, bound, _, _ = WORKLOADS[name]
     sel = {"model": 0, "cogent": 1, "ttgt": 2}[args.backend]
-    local_eq = tc.TCEquation(mC, mA, mB, dict(ext), "-", tc.ScalarType(st), tc.BackendSelection(sel))
-    global_eq = sharding.grow_equation(local_eq, shard_mode, world)
-    # every rank generates its own slice of the global inputs: the sharded operand at the
-    # rank's offset of the stream, the shared operand identically everywhere
+    full_eq = tc.TCEquation(mC, mA, mB, dict(ext), "-", tc.ScalarType(st), tc.BackendSelection(sel))
+    contracted = args.split == "contracted"
+    if contracted:
+        args.scaling = "strong"
+        shard_mode = args.split_mode or next(m for m in mA if m not in mC)
+        local_eq, _ = sharding.shard_contracted(full_eq, shard_mode, world, rank)
+        global_eq = full_eq
+    elif args.scaling == "strong":
+        shard_mode = args.split_mode or shard_mode
+        local_eq, _ = sharding.shard_equation(full_eq, shard_mode, world, rank)
+        global_eq = full_eq
+    else:
+        shard_mode = args.split_mode or shard_mode
+        local_eq = full_eq
+        global_eq = sharding.grow_equation(local_eq, shard_mode, world)
+    # every rank generates its own slice of the global inputs: a sharded operand at the rank's
+    # offset of the stream, a shared operand identically everywhere
     nA, nB = local_eq.size(mA), local_eq.size(mB)
-    a_sharded = shard_mode in mA
+    a_sharded, b_sharded = shard_mode in mA, shard_mode in mB
     A = tc.fill_uniform(nA, local_eq.scalar_type, seed, rank * nA if a_sharded else 0, lo, hi)
     offB = world * nA if a_sharded else nA
-    B = tc.fill_uniform(nB, local_eq.scalar_type, seed, offB + (0 if a_sharded else rank * nB), lo, hi)
+    B = tc.fill_uniform(nB, local_eq.scalar_type, seed, offB + (rank * nB if b_sharded else 0), lo, hi)
     plan = tc.plan(local_eq)
-    run = tc.prepare(plan, A, B)
     desc = plan.describe()
+    nC = local_eq.size(mC)
+    if contracted:
+        # partial C and the reduce-scatter output live in torch tensors; the engine works on them in
+        # place on torch's current stream, so the NCCL call is ordered behind the kernel
+        dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+        partial = torch.empty(nC, dtype=dA.dtype, device="cuda")
+        reduced = torch.empty(nC // world, dtype=dA.dtype, device="cuda")
+        run = api.prepare_on_device(plan, dA.data_ptr(), dB.data_ptr(), partial.data_ptr(), keep=(dA, dB, partial))
+        run.set_stream(torch.cuda.current_stream().cuda_stream)
+    else:
+        run = tc.prepare(plan, A, B)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -214,12 +247,27 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    tc.warmup(run, max(args.warmup, 3))
+    def step():
+        tc.launch(run)
+        if contracted and world > 1:
+            dist.reduce_scatter_tensor(reduced, partial)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
     sampler = ClockSampler()
     if rank == 0:
         sampler.start()
     sync_all()
-    ms, launches = run.time_launches(args.steps)
+    if contracted:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms, launches = e0.elapsed_time(e1), args.steps * (1 + int(desc["transpose_a"] is not None) + int(desc["transpose_b"] is not None))
+    else:
+        ms, launches = run.time_launches(args.steps)
     sync_all()
     clocks = sampler.stop(set(range(world))) if rank == 0 else None
     if run.device_status() != 0:
@@ -231,11 +279,15 @@ def main():
     ms_step = ms_total / args.steps
     flops_local = plan.flops
     value = world * flops_local / (ms_step * 1e-3) / 1e12
+    if contracted:
+        nccl_bytes = (world - 1) / world * nC * (8 if st else 4)   # leaves each GPU in the reduce-scatter
 
     # end to end through the host-buffer entry point: pinned host A, B -> device, launch, C -> pinned host
     hA = torch.from_numpy(A).pin_memory()
     hB = torch.from_numpy(B).pin_memory()
     hC = torch.empty(local_eq.size(mC), dtype=hA.dtype).pin_memory()
+    if contracted:
+        run = tc.prepare(plan, A, B)   # the end-to-end leg measures the host-buffer entry point of one rank's share
     run.contract_host_ptr(hA.data_ptr(), hB.data_ptr(), hC.data_ptr())
     sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -256,32 +308,45 @@ def main():
         peaks = measured_peaks()
         elt = 8 if st else 4
         alg_bytes = (nA + nB + local_eq.size(mC)) * elt
+        extra = {}
         if bound == "tensor":
-            # TF32 dense rate is half the bf16 rate of the same tensor cores; FP64 has no measured
-            # entry in the peaks file, so an FP64 tensor-bound workload reports against HBM instead.
-            peak = peaks["bf16_tflops"] / 2.0 if st == 0 else None
             achieved = flops_local / (ms_step * 1e-3) / 1e12
             unit = "TFLOP/s"
-        if bound == "hbm" or peak is None:
+            if st == 0:
+                # TF32 dense rate is half the bf16 rate of the same tensor cores
+                peak = peaks["bf16_tflops"] / 2.0
+                source = peaks["source"] + " bf16 dense / 2 (TF32 rate)"
+                try:
+                    extra["tcgen05_tf32_peak_microbenchmark"] = api.measure_peak("tf32")
+                except Exception:
+                    pass
+            else:
+                # the peaks file has no FP64 entry: measured here, mma.sync m8n8k4 on every SM at once
+                peak = max(api.measure_peak("fp64_dmma"), api.measure_peak("fp64_dfma"))
+                source = "FP64 microbenchmark run by this process (max of mma.sync m8n8k4 and DFMA)"
+                extra["hbm_write_floor_ms"] = local_eq.size(mC) * elt / (peaks["hbm_gbs"] * 1e9) * 1e3
+            bound_used = "tensor"
+        else:
             bound_used, peak, unit = "hbm", peaks["hbm_gbs"], "GB/s"
             achieved = alg_bytes / (ms_step * 1e-3) / 1e9
-        else:
-            bound_used = "tensor"
+            source = peaks["source"] + " copy bandwidth"
         roofline = {"bound": bound_used, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                    "traffic": None, "kernel": desc["kernel"], "peak_source": peaks["source"] +
-                    (" bf16 dense / 2 (TF32 rate)" if bound_used == "tensor" else " copy bandwidth"),
-                    "algorithmic_bytes_per_launch": alg_bytes, "flops_per_launch": flops_local}
+                    "traffic": NCU_TRAFFIC.get(name), "kernel": desc["kernel"], "peak_source": source,
+                    "algorithmic_bytes_per_launch": alg_bytes, "flops_per_launch": flops_local, **extra}
         line = {"metric": "contraction throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
                 "vs_baseline": None, "dtype": "f64" if st else "tf32", "data": "synthetic",
                 "config": {"workload": describe(name), "global": {shard_mode: int(global_eq.extent[shard_mode])},
-                           "sharded_mode": shard_mode, "backend": desc["backend"], "kernel": desc["kernel"],
+                           "sharded_mode": shard_mode, "split": args.split, "backend": desc["backend"], "kernel": desc["kernel"],
                            "l2": "inputs and output exceed the 126 MB L2" if alg_bytes > 126e6 else "working set fits L2",
                            "timing": "CUDA events on the launching stream, max over ranks"},
                 "clocks": clocks, "gpu_launches": int(launches),
                 "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                         "ms_per_step": e2e_ms, "checksum": checksum},
                 "roofline": roofline}
+        if contracted:
+            line["config"]["collective"] = {"op": "ncclReduceScatter sum over NVLink, after every launch, inside the timed region",
+                                            "bytes_sent_per_gpu_per_step": int(nccl_bytes)}
         if world == 1 and not args.no_cpu_baseline:
             info, _ = cpu_baseline(name)
             line["cpu_baseline"] = info

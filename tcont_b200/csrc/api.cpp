@@ -270,6 +270,17 @@ tcontb_status finish_run(tcontb_run* run)
                     if (v & 1) return false;
                 return true;
             };
+            // K-major operand: neighbouring k neighbours in memory, every row offset even
+            auto kpairs_ok = [](const std::vector<int64_t>& row, const std::vector<int64_t>& k) {
+                if (k.size() % 2) return false;
+                for (size_t i = 0; i < k.size(); i += 2)
+                    if ((k[i] & 1) || k[i + 1] != k[i] + 1) return false;
+                for (int64_t v : row)
+                    if (v & 1) return false;
+                return true;
+            };
+            if (run->simt.a_along_k == 1 && kpairs_ok(t.offAm, t.offAk) && reinterpret_cast<uintptr_t>(kA) % 16 == 0) run->simt.a_along_k = 3;
+            if (run->simt.b_along_k == 1 && kpairs_ok(t.offBn, t.offBk) && reinterpret_cast<uintptr_t>(kB) % 16 == 0) run->simt.b_along_k = 3;
             if (run->simt.a_along_k == 0 && pairs_ok(t.offAm, t.offAk) && reinterpret_cast<uintptr_t>(kA) % 16 == 0) run->simt.a_along_k = 2;
             if (run->simt.b_along_k == 0 && pairs_ok(t.offBn, t.offBk) && reinterpret_cast<uintptr_t>(kB) % 16 == 0) run->simt.b_along_k = 2;
         }

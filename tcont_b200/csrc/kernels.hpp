@@ -21,7 +21,7 @@ struct SimtParams {
     const int64_t* offBk;
     const int64_t* offCm;
     const int64_t* offCn;
-    int a_along_k, b_along_k;  // 0: threads run along the rows, 1: along k, 2 (FP64 tensor kernel only): along the rows, two at a time
+    int a_along_k, b_along_k;  // 0: threads run along the rows, 1: along k, 2 / 3 (FP64 tensor kernel only): along the rows / along k, two at a time
 };
 cudaError_t launch_simt_contract(const SimtParams& p, int scalar_type, cudaStream_t stream);
 

@@ -474,7 +474,8 @@ int pick_kernel(const Problem& p, const UmmaSpec& u)
     if (u.eligible) return KERNEL_UMMA_TF32;
     const char* k = std::getenv("TCONT_KERNEL");
     const bool simt_only = k && std::strcmp(k, "simt") == 0;
-    if (p.scalar_type == 1 && !simt_only && ceil_div(p.Mtot, 128) * ceil_div(p.Ntot, 128) >= 148) return KERNEL_DMMA_F64;
+    const int64_t bn = p.Ntot <= 48 ? 32 : 64, bm = p.Ntot <= 48 ? 256 : 128;  // the tensor-path kernel's smallest fitting tile
+    if (p.scalar_type == 1 && !simt_only && ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn) >= 148) return KERNEL_DMMA_F64;
     return KERNEL_SIMT;
 }
 

@@ -54,3 +54,18 @@ def put_slice(dst: np.ndarray, part: np.ndarray, modes: str, extent: dict, mode:
     local_shape = list(shape)
     local_shape[axis] = sl.stop - sl.start
     nd[tuple(index)] = part.reshape(local_shape)
+
+
+def shard_contracted(eq, mode: str, world: int, rank: int):
+    """Cut a CONTRACTED mode: every rank sums over its slice of `mode` and produces a full-size
+    partial C; the partials must then be added (reduce-scatter over NVLink leaves each rank with
+    1/world of C).  Returns the local descriptor and the slice of `mode` the rank owns."""
+    if mode in eq.modeC or mode not in eq.modeA or mode not in eq.modeB:
+        raise ValueError(f"mode '{mode}' is not a contracted mode of this contraction")
+    full = int(eq.extent[mode])
+    if full % world:
+        raise ValueError(f"extent {full} of mode '{mode}' does not divide over {world} ranks")
+    local = full // world
+    ext = dict(eq.extent)
+    ext[mode] = local
+    return replace(eq, extent=ext), slice(rank * local, (rank + 1) * local)
