@@ -176,6 +176,9 @@ def main():
     ap.add_argument("--backend", default="model", choices=["model", "cogent", "ttgt"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--extent", action="append", default=[], metavar="MODE=N",
+                    help="override one extent of the workload (repeatable), e.g. --workload cfg3 --extent k=4 for a "
+                         "case small enough to profile; the JSON line then names the changed extents")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: the global problem grows with N (default); strong: the named configuration is cut into N slices")
     ap.add_argument("--split", default="external", choices=["external", "contracted"],
@@ -205,6 +208,12 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     mC, mA, mB, ext, st, seed, lo, hi, shard_mode, bound, _, _ = WORKLOADS[name]
+    ext = dict(ext)
+    for ov in args.extent:
+        m, v = ov.split("=")
+        if m not in ext:
+            raise SystemExit(f"--extent: workload {name} has no mode '{m}'")
+        ext[m] = int(v)
     sel = {"model": 0, "cogent": 1, "ttgt": 2}[args.backend]
     full_eq = tc.TCEquation(mC, mA, mB, dict(ext), "-", tc.ScalarType(st), tc.BackendSelection(sel))
     contracted = args.split == "contracted"
@@ -337,7 +346,7 @@ def main():
         line = {"metric": "contraction throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
                 "vs_baseline": None, "dtype": "f64" if st else "tf32", "data": "synthetic",
-                "config": {"workload": describe(name), "global": {shard_mode: int(global_eq.extent[shard_mode])},
+                "config": {"workload": describe(name) + (" with " + ",".join(args.extent) if args.extent else ""), "global": {shard_mode: int(global_eq.extent[shard_mode])},
                            "sharded_mode": shard_mode, "split": args.split, "backend": desc["backend"], "kernel": desc["kernel"],
                            "l2": "inputs and output exceed the 126 MB L2" if alg_bytes > 126e6 else "working set fits L2",
                            "timing": "CUDA events on the launching stream, max over ranks"},
@@ -348,7 +357,7 @@ def main():
         if contracted:
             line["config"]["collective"] = {"op": "ncclReduceScatter sum over NVLink, after every launch, inside the timed region",
                                             "bytes_sent_per_gpu_per_step": int(nccl_bytes)}
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.extent:
             info, _ = cpu_baseline(name)
             line["cpu_baseline"] = info
         print(json.dumps(line), flush=True)

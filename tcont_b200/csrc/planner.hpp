@@ -96,7 +96,7 @@ struct SimtSpec {
 };
 
 struct CostTable {
-    // Measured on B200 (see profiles/); overridable through the file named by TCONT_COST_TABLE.
+    // Measured on B200; overridable through the file named by TCONT_COST_TABLE ("key value" lines).
     double hbm_gbs = 6546.9;
     double umma_tf32_tflops = 600.0;
     double simt_f32_tflops = 20.0;
