@@ -98,9 +98,22 @@ struct tcontb_run {
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     bool ev_valid = false;
     int64_t kernels_per_launch = 0;
+    // Several GPUs of one box behind one run (TCONT_NUM_GPUS > 1): the contraction is cut along an
+    // external mode, shard g lives on device first_device + g and is an ordinary run of the
+    // smaller contraction; this object then only keeps the global host inputs.
+    std::vector<std::unique_ptr<tcontb_run>> shards;
+    std::vector<cudaEvent_t> shard_done;
+    int first_device = 0;
+    char split_mode = 0;
 
     ~tcontb_run()
     {
+        for (size_t g = 0; g < shards.size(); ++g) {
+            cudaSetDevice(first_device + static_cast<int>(g));
+            shards[g].reset();
+            if (g < shard_done.size() && shard_done[g]) cudaEventDestroy(shard_done[g]);
+        }
+        if (!shard_done.empty()) cudaSetDevice(first_device);
         if (prof.ptr) {
             // Tuning aid: mean cycles per CTA spent in each role's waits during the last launch.
             std::vector<long long> h(static_cast<size_t>(num_sms) * 8);
@@ -327,6 +340,109 @@ tcontb_status new_run(const tcontb_plan* plan, std::unique_ptr<tcontb_run>* out)
     return TCONTB_OK;
 }
 
+// Copies the slice [lo, lo+len) of `mode` out of (or, with scatter = true, back into) a
+// column-major tensor: `full` has the global extents, `part` the sliced one.
+void slice_mode(unsigned char* full, unsigned char* part, const std::string& modes, const Plan& pl, char mode, int64_t lo,
+                int64_t len, size_t elt, bool scatter)
+{
+    const size_t pos = modes.find(mode);
+    auto ext = [&](char c) { return pl.ext_val[pl.ext_mode.find(c)]; };
+    int64_t inner = 1, outer = 1;
+    for (size_t i = 0; i < modes.size(); ++i) {
+        if (i < pos) inner *= ext(modes[i]);
+        else if (i > pos) outer *= ext(modes[i]);
+    }
+    const int64_t e = ext(mode);
+    const size_t run_bytes = static_cast<size_t>(len * inner) * elt;
+    for (int64_t o = 0; o < outer; ++o) {
+        unsigned char* f = full + static_cast<size_t>((o * e + lo) * inner) * elt;
+        unsigned char* q = part + static_cast<size_t>(o * len * inner) * elt;
+        if (scatter) std::memcpy(f, q, run_bytes);
+        else std::memcpy(q, f, run_bytes);
+    }
+}
+
+int requested_gpus()
+{
+    const char* e = std::getenv("TCONT_NUM_GPUS");
+    const int g = e ? std::atoi(e) : 1;
+    return g > 1 ? g : 1;
+}
+
+// Builds the shards of a multi-GPU run; `run` already holds the global plan and host inputs.
+// Returns TCONTB_OK with run->shards empty when no external mode divides over the GPUs.
+tcontb_status make_shards(tcontb_run* run, int gpus)
+{
+    const Plan& pl = run->plan;
+    int have = 0;
+    TC_CUDA(cudaGetDeviceCount(&have));
+    TC_CUDA(cudaGetDevice(&run->first_device));
+    if (run->first_device + gpus > have)
+        return fail(TCONTB_RUNTIME_ERROR, "TCONT_NUM_GPUS asks for more devices than the box has from the current device on");
+    auto external = [&](char c) {
+        return pl.modeC.find(c) != std::string::npos && ((pl.modeA.find(c) != std::string::npos) != (pl.modeB.find(c) != std::string::npos));
+    };
+    auto ext = [&](char c) { return pl.ext_val[pl.ext_mode.find(c)]; };
+    char mode = 0;
+    if (const char* sp = std::getenv("TCONT_SPLIT")) {  // "ext:<mode>"
+        if (std::strncmp(sp, "ext:", 4) != 0 || !sp[4] || !external(sp[4]) || ext(sp[4]) % gpus)
+            return fail(TCONTB_INVALID_ARGUMENT, "TCONT_SPLIT must be ext:<mode> naming an external mode whose extent divides over the GPUs");
+        mode = sp[4];
+    } else {
+        // slowest mode of C first: its slices are contiguous blocks of C
+        for (size_t i = pl.modeC.size(); i-- > 0 && !mode;)
+            if (external(pl.modeC[i]) && ext(pl.modeC[i]) % gpus == 0) mode = pl.modeC[i];
+        if (!mode) return TCONTB_OK;
+    }
+    run->split_mode = mode;
+    const int64_t len = ext(mode) / gpus;
+    std::vector<int64_t> local_ext = pl.ext_val;
+    local_ext[pl.ext_mode.find(mode)] = len;
+    const bool in_a = pl.modeA.find(mode) != std::string::npos;
+    for (int g = 0; g < gpus; ++g) {
+        TC_CUDA(cudaSetDevice(run->first_device + g));
+        std::unique_ptr<tcontb_run> sh(new tcontb_run());
+        std::string err;
+        const int rc = make_plan(pl.modeC.data(), static_cast<int>(pl.modeC.size()), pl.modeA.data(), static_cast<int>(pl.modeA.size()),
+                                 pl.modeB.data(), static_cast<int>(pl.modeB.size()), pl.op, pl.scalar_type, pl.ext_mode.data(),
+                                 local_ext.data(), static_cast<int>(local_ext.size()), pl.backend_selection, load_cost_table(),
+                                 &sh->plan, &err);
+        if (rc) return fail(static_cast<tcontb_status>(rc), err);
+        sh->elt = run->elt;
+        const size_t bl = static_cast<size_t>(sh->plan.sizeL) * run->elt, br = static_cast<size_t>(sh->plan.sizeR) * run->elt;
+        sh->hL.resize(bl);
+        sh->hR.resize(br);
+        if (in_a) {
+            slice_mode(run->hL.data(), sh->hL.data(), pl.modeA, pl, mode, g * len, len, run->elt, false);
+            sh->hR = run->hR;
+        } else {
+            sh->hL = run->hL;
+            slice_mode(run->hR.data(), sh->hR.data(), pl.modeB, pl, mode, g * len, len, run->elt, false);
+        }
+        tcontb_status st = alloc_owned(sh.get());
+        if (st != TCONTB_OK) return st;
+        TC_CUDA(cudaMemcpy(sh->dL, sh->hL.data(), bl, cudaMemcpyHostToDevice));
+        TC_CUDA(cudaMemcpy(sh->dR, sh->hR.data(), br, cudaMemcpyHostToDevice));
+        sh->hL.clear();
+        sh->hL.shrink_to_fit();
+        sh->hR.clear();
+        sh->hR.shrink_to_fit();
+        st = finish_run(sh.get());
+        if (st != TCONTB_OK) return st;
+        cudaEvent_t ev = nullptr;
+        TC_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        run->shard_done.push_back(ev);
+        run->shards.push_back(std::move(sh));
+    }
+    TC_CUDA(cudaSetDevice(run->first_device));
+    run->kernels_per_launch = 0;
+    for (auto& sh : run->shards) run->kernels_per_launch += sh->kernels_per_launch;
+    return TCONTB_OK;
+}
+
+#define TC_NOT_SHARDED(run, what)                                                                              \
+    if (!(run)->shards.empty()) return fail(TCONTB_UNSUPPORTED, what " is not available on a multi-GPU run")
+
 }  // namespace
 
 extern "C" {
@@ -386,6 +502,14 @@ tcontb_status tcontb_run_create_with_inputs(const tcontb_plan* plan, const void*
     run->hL.assign(static_cast<const unsigned char*>(a_host), static_cast<const unsigned char*>(a_host) + bl);
     run->hR.assign(static_cast<const unsigned char*>(b_host), static_cast<const unsigned char*>(b_host) + br);
     run->has_host = true;
+    if (requested_gpus() > 1) {
+        st = make_shards(run.get(), requested_gpus());
+        if (st != TCONTB_OK) return st;
+        if (!run->shards.empty()) {
+            *out = run.release();
+            return TCONTB_OK;
+        }
+    }
     st = alloc_owned(run.get());
     if (st != TCONTB_OK) return st;
     TC_CUDA(cudaMemcpy(run->dL, run->hL.data(), bl, cudaMemcpyHostToDevice));
@@ -438,6 +562,7 @@ void tcontb_run_destroy(tcontb_run* run) { delete run; }
 tcontb_status tcontb_run_set_stream(tcontb_run* run, void* cuda_stream)
 {
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    TC_NOT_SHARDED(run, "a caller stream");
     run->stream = static_cast<cudaStream_t>(cuda_stream);
     return TCONTB_OK;
 }
@@ -446,6 +571,7 @@ tcontb_status tcontb_run_upload_inputs(tcontb_run* run, const void* a_host, cons
 {
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
     if (!a_host || !b_host) return fail(TCONTB_INVALID_ARGUMENT, "Null input buffer");
+    TC_NOT_SHARDED(run, "replacing the inputs");
     const Plan& pl = run->plan;
     TC_CUDA(cudaMemcpyAsync(run->dL, a_host, static_cast<size_t>(pl.sizeL) * run->elt, cudaMemcpyHostToDevice, run->stream));
     TC_CUDA(cudaMemcpyAsync(run->dR, b_host, static_cast<size_t>(pl.sizeR) * run->elt, cudaMemcpyHostToDevice, run->stream));
@@ -455,6 +581,22 @@ tcontb_status tcontb_run_upload_inputs(tcontb_run* run, const void* a_host, cons
 tcontb_status tcontb_run_launch(tcontb_run* run)
 {
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    if (!run->shards.empty()) {
+        // Every shard runs on its own device's NULL stream; the first device's NULL stream then waits
+        // for all of them, so events the caller records there bracket the whole multi-GPU launch.
+        for (size_t g = 0; g < run->shards.size(); ++g) {
+            TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
+            const tcontb_status st = tcontb_run_launch(run->shards[g].get());
+            if (st != TCONTB_OK) {
+                cudaSetDevice(run->first_device);
+                return st;
+            }
+            TC_CUDA(cudaEventRecord(run->shard_done[g], nullptr));
+        }
+        TC_CUDA(cudaSetDevice(run->first_device));
+        for (size_t g = 1; g < run->shards.size(); ++g) TC_CUDA(cudaStreamWaitEvent(nullptr, run->shard_done[g], 0));
+        return TCONTB_OK;
+    }
     const Plan& pl = run->plan;
     const bool t = run->stage_timing;
     if (t) TC_CUDA(cudaEventRecord(run->ev[0], run->stream));
@@ -482,6 +624,11 @@ tcontb_status tcontb_run_warmup(tcontb_run* run, int iterations)
         const tcontb_status st = tcontb_run_launch(run);
         if (st != TCONTB_OK) return st;
     }
+    for (size_t g = 0; g < run->shards.size(); ++g) {
+        TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
+        TC_CUDA(cudaDeviceSynchronize());
+    }
+    if (!run->shards.empty()) TC_CUDA(cudaSetDevice(run->first_device));
     TC_CUDA(cudaDeviceSynchronize());
     return TCONTB_OK;
 }
@@ -489,6 +636,15 @@ tcontb_status tcontb_run_warmup(tcontb_run* run, int iterations)
 tcontb_status tcontb_run_zero_output(tcontb_run* run)
 {
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    if (!run->shards.empty()) {
+        for (size_t g = 0; g < run->shards.size(); ++g) {
+            TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
+            const tcontb_status st = tcontb_run_zero_output(run->shards[g].get());
+            if (st != TCONTB_OK) return st;
+        }
+        TC_CUDA(cudaSetDevice(run->first_device));
+        return TCONTB_OK;
+    }
     TC_CUDA(cudaMemsetAsync(run->dC, 0, static_cast<size_t>(run->plan.sizeC) * run->elt, run->stream));
     return TCONTB_OK;
 }
@@ -497,6 +653,7 @@ tcontb_status tcontb_run_stage_times(tcontb_run* run, float out[6])
 {
     if (!run || !out) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
     for (int i = 0; i < 6; ++i) out[i] = 0.0f;
+    if (!run->shards.empty()) return tcontb_run_stage_times(run->shards[0].get(), out);  // the first device's stages
     if (!run->stage_timing || !run->ev_valid) return TCONTB_OK;
     TC_CUDA(cudaEventSynchronize(run->ev[3]));
     float ta = 0, tb = 0, tc = 0;
@@ -524,6 +681,23 @@ tcontb_status tcontb_run_copy_output(tcontb_run* run, void* dst, size_t bytes)
     if (!dst) return fail(TCONTB_INVALID_ARGUMENT, "Destination buffer is null");
     const size_t have = static_cast<size_t>(run->plan.sizeC) * run->elt;
     if (bytes > have) return fail(TCONTB_INVALID_ARGUMENT, "Requested more bytes than the output tensor holds");
+    if (!run->shards.empty()) {
+        // gather: every shard's C goes back to its slice of the global tensor
+        if (bytes != have) return fail(TCONTB_INVALID_ARGUMENT, "A multi-GPU run copies the whole output tensor or nothing");
+        const Plan& pl = run->plan;
+        const int64_t len = pl.ext_val[pl.ext_mode.find(run->split_mode)] / static_cast<int64_t>(run->shards.size());
+        std::vector<unsigned char> part;
+        for (size_t g = 0; g < run->shards.size(); ++g) {
+            tcontb_run* sh = run->shards[g].get();
+            part.resize(static_cast<size_t>(sh->plan.sizeC) * run->elt);
+            TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
+            TC_CUDA(cudaMemcpy(part.data(), sh->dC, part.size(), cudaMemcpyDeviceToHost));
+            slice_mode(static_cast<unsigned char*>(dst), part.data(), pl.modeC, pl, run->split_mode, static_cast<int64_t>(g) * len, len,
+                       run->elt, true);
+        }
+        TC_CUDA(cudaSetDevice(run->first_device));
+        return TCONTB_OK;
+    }
     TC_CUDA(cudaMemcpyAsync(dst, run->dC, bytes, cudaMemcpyDeviceToHost, run->stream));
     TC_CUDA(cudaStreamSynchronize(run->stream));
     return TCONTB_OK;
@@ -554,6 +728,7 @@ tcontb_status tcontb_run_contract_host(tcontb_run* run, const void* a_host, cons
 {
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
     if (!c_host) return fail(TCONTB_INVALID_ARGUMENT, "Destination buffer is null");
+    TC_NOT_SHARDED(run, "the host-buffer pass");
     tcontb_status st = tcontb_run_upload_inputs(run, a_host, b_host);
     if (st != TCONTB_OK) return st;
     st = tcontb_run_launch(run);
@@ -569,6 +744,18 @@ tcontb_status tcontb_run_contract_host(tcontb_run* run, const void* a_host, cons
 tcontb_status tcontb_run_device_status(tcontb_run* run, int* status)
 {
     if (!run || !status) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    if (!run->shards.empty()) {
+        *status = 0;
+        for (size_t g = 0; g < run->shards.size(); ++g) {
+            int s1 = 0;
+            TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
+            const tcontb_status st = tcontb_run_device_status(run->shards[g].get(), &s1);
+            if (st != TCONTB_OK) return st;
+            if (s1 > *status) *status = s1;
+        }
+        TC_CUDA(cudaSetDevice(run->first_device));
+        return TCONTB_OK;
+    }
     TC_CUDA(cudaMemcpyAsync(status, run->status.ptr, sizeof(int), cudaMemcpyDeviceToHost, run->stream));
     TC_CUDA(cudaStreamSynchronize(run->stream));
     return TCONTB_OK;
