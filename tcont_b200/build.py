@@ -19,9 +19,9 @@ OBJ = os.path.join(PKG, "_build")
 LIB_C = os.path.join(PKG, "libtcontb.so")
 LIB_CPP = os.path.join(PKG, "libtcont.so")
 
-CORE_SOURCES = ["planner.cpp", "api.cpp", "simt_contract.cu", "dmma_f64.cu", "transpose.cu", "umma_tf32.cu", "no_alloc.cu", "peaks.cu"]
+CORE_SOURCES = ["planner.cpp", "api.cpp", "simt_contract.cu", "dmma_f64.cu", "dmma_tma_f64.cu", "transpose.cu", "umma_tf32.cu", "no_alloc.cu", "peaks.cu"]
 SHIM_SOURCES = ["tcont_shim.cpp"]
-HEADERS = ["planner.hpp", "kernels.hpp", os.path.join(ROOT, "include", "tcontb.h"), os.path.join(ROOT, "include", "tcont.hpp"),
+HEADERS = ["planner.hpp", "kernels.hpp", "tile_common.cuh", os.path.join(ROOT, "include", "tcontb.h"), os.path.join(ROOT, "include", "tcont.hpp"),
            os.path.join(ROOT, "include", "tcont_b200", "tcont_api.hpp")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",

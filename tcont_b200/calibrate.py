@@ -1,0 +1,102 @@
+"""Fills the planner's cost table from measurements on the current GPU and writes it as the
+"key value" file that TCONT_COST_TABLE names.
+
+    python -m tcont_b200.calibrate [-o cost_table.txt]
+
+The reference decides between its two backends with a LightGBM model trained offline on A100
+runs (final_model/*.json, src/backend_model_selector.cpp:365-403); the trainer is not part of its
+tree.  Here the decision is an explicit time estimate per route, and these are its constants:
+copy bandwidth, the rate of each contraction kernel on a large well-shaped problem, the launch
+overhead, and the penalty for TMA boxes whose rows lie far apart in memory.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+
+
+def _rate(tc, api, torch, modes, extent, scalar, iters=10, env=None):
+    old = {}
+    for k, v in (env or {}).items():
+        old[k] = os.environ.get(k)
+        os.environ[k] = v
+    try:
+        eq = tc.TCEquation(*modes, dict(extent), "-", scalar, tc.BackendSelection.COGENT)
+        plan = tc.plan(eq)
+        dt = torch.float64 if scalar == tc.ScalarType.Float64 else torch.float32
+        a = torch.rand(eq.size(eq.modeA), device="cuda", dtype=dt) - 0.5
+        b = torch.rand(eq.size(eq.modeB), device="cuda", dtype=dt) - 0.5
+        c = torch.empty(eq.size(eq.modeC), device="cuda", dtype=dt)
+        run = api.prepare_on_device(plan, a.data_ptr(), b.data_ptr(), c.data_ptr(), keep=(a, b, c))
+        tc.warmup(run, 3)
+        ms, _ = run.time_launches(iters)
+        return plan.flops / (ms / iters * 1e-3) / 1e12, plan.describe()["kernel"]
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+
+
+def calibrate() -> dict:
+    import torch
+
+    import tcont_b200 as tc
+    from tcont_b200 import api
+
+    F32, F64 = tc.ScalarType.Float32, tc.ScalarType.Float64
+    table = {}
+    # copy bandwidth through the permutation kernel with an identity permutation (read + write)
+    n = 1 << 28
+    src = torch.empty(n, device="cuda", dtype=torch.float32)
+    dst = torch.empty_like(src)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        api.transpose(src.data_ptr(), dst.data_ptr(), [n // 1024, 1024], [0, 1], 4, stream)
+    e0.record()
+    for _ in range(10):
+        api.transpose(src.data_ptr(), dst.data_ptr(), [n // 1024, 1024], [0, 1], 4, stream)
+    e1.record()
+    torch.cuda.synchronize()
+    table["hbm_gbs"] = 2 * n * 4 * 10 / (e0.elapsed_time(e1) * 1e-3) / 1e9
+    del src, dst
+    gemm = (("ab", "ka", "kb"), dict(a=8192, b=8192, k=4096))
+    table["umma_tf32_tflops"], k = _rate(tc, api, torch, *gemm, F32)
+    assert k == "umma_tf32", k
+    table["simt_f32_tflops"], _ = _rate(tc, api, torch, ("ab", "ka", "kb"), dict(a=4096, b=4096, k=1024), F32, env={"TCONT_KERNEL": "simt"})
+    table["dmma_f64_tflops"], k = _rate(tc, api, torch, ("ab", "ak", "bk"), dict(a=4096, b=4096, k=2048), F64)
+    assert k == "dmma_f64", k
+    table["simt_f64_tflops"], _ = _rate(tc, api, torch, ("ab", "ak", "bk"), dict(a=4096, b=4096, k=1024), F64, env={"TCONT_KERNEL": "simt"})
+    # far-row penalty: the same 4-D contraction with the chunked contracted mode near (f) and far (e) in B
+    shape = (("abcd", "aebf", "cfde"), dict(a=128, b=64, c=128, d=64, e=64, f=64))
+    near, _ = _rate(tc, api, torch, *shape, F32, iters=3, env={"TCONT_UMMA_KC": "f"})
+    far, _ = _rate(tc, api, torch, *shape, F32, iters=3, env={"TCONT_UMMA_KC": "e"})
+    # kc=f: A's rows are far (1/3 of a stage's bytes); kc=e: B's rows are far (2/3): rate ~ 1 - p * share
+    table["far_row_penalty"] = max(0.0, min(1.0, (near - far) / max(near * (2 / 3) - far * (1 / 3), 1e-9)))
+    # launch overhead: a contraction too small to matter
+    eq = tc.TCEquation("ab", "ak", "kb", dict(a=64, b=64, k=8), "-", F64, tc.BackendSelection.COGENT)
+    a = torch.zeros(512, device="cuda", dtype=torch.float64)
+    c = torch.zeros(4096, device="cuda", dtype=torch.float64)
+    run = api.prepare_on_device(tc.plan(eq), a.data_ptr(), a.data_ptr(), c.data_ptr(), keep=(a, c))
+    tc.warmup(run, 10)
+    ms, _ = run.time_launches(200)
+    table["launch_us"] = ms / 200 * 1e3
+    return table
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("-o", "--output", default="tcont_cost_table.txt")
+    args = ap.parse_args()
+    table = calibrate()
+    with open(args.output, "w") as f:
+        for k, v in table.items():
+            f.write(f"{k} {v:.6g}\n")
+            print(f"{k} {v:.6g}")
+    print(f"wrote {args.output}; use it with TCONT_COST_TABLE={args.output}")
+
+
+if __name__ == "__main__":
+    main()

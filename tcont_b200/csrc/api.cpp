@@ -125,7 +125,11 @@ struct tcontb_run {
                         ++n;
                         for (int i = 0; i < 8; ++i) s[i] += double(h[static_cast<size_t>(b) * 8 + i]);
                     }
-                if (n)
+                if (n && plan.kernel == KERNEL_DMMA_F64_TMA)
+                    std::fprintf(stderr, "[tcontb prof] ctas=%d group0_total=%.0f wait_stage_full=%.0f main_loop=%.0f tables=%.0f "
+                                 "stores=%.0f token_wait=%.0f (cycles, mean per CTA, consumer group 0)\n",
+                                 n, s[0] / n, s[1] / n, s[2] / n, s[3] / n, s[4] / n, s[5] / n);
+                else if (n)
                     std::fprintf(stderr, "[tcontb prof] ctas=%d mma_total=%.0f mma_wait_acc_empty=%.0f mma_wait_stage_full=%.0f "
                                  "producer_wait_stage_empty=%.0f epilogue_total=%.0f epilogue_wait_acc_full=%.0f (cycles, mean per CTA; MMA figures over issuing CTAs)\n",
                                  n, s[0] / n, s[1] / n, s[2] / n, s[3] / n, s[4] / n, s[5] / n);
@@ -161,7 +165,7 @@ void fill_operand_dev(const UmmaOperand& o, UmmaOperandDev* d)
     for (int i = 0; i < 3; ++i) d->k_digit_dim[i] = o.k_digit_dim[i];
 }
 
-tcontb_status encode_map(const UmmaOperand& o, const void* base, CUtensorMap* out)
+tcontb_status encode_map(const UmmaOperand& o, const void* base, int elt, CUtensorMap* out)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(TCONTB_RUNTIME_ERROR, "cuTensorMapEncodeTiled is not available from the CUDA driver");
@@ -172,12 +176,12 @@ tcontb_status encode_map(const UmmaOperand& o, const void* base, CUtensorMap* ou
         dims[d] = static_cast<cuuint64_t>(o.ext[d]);
         box[d] = static_cast<cuuint32_t>(o.box[d]);
         estr[d] = 1;
-        if (d > 0) strides[d - 1] = static_cast<cuuint64_t>(o.stride[d]) * 4u;
+        if (d > 0) strides[d - 1] = static_cast<cuuint64_t>(o.stride[d]) * static_cast<cuuint64_t>(elt);
     }
-    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, kMaxTmaRank, const_cast<void*>(base), dims, strides, box, estr,
+    const CUresult r = fn(out, elt == 8 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT64 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, kMaxTmaRank, const_cast<void*>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE,
                           // an MN-major 32-bit operand must be swizzled in 32-byte units for tcgen05.mma
-                          o.major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          (o.major && elt == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TCONTB_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
@@ -213,7 +217,7 @@ tcontb_status finish_run(tcontb_run* run)
     TC_CUDA(run->status.alloc(sizeof(int)));
     TC_CUDA(cudaMemset(run->status.ptr, 0, sizeof(int)));
 
-    if (pl.kernel == KERNEL_UMMA_TF32) {
+    if (pl.kernel == KERNEL_UMMA_TF32 || pl.kernel == KERNEL_DMMA_F64_TMA) {
         const UmmaSpec& u = pl.umma;
         fill_operand_dev(u.a, &run->umma.a);
         fill_operand_dev(u.b, &run->umma.b);
@@ -228,6 +232,7 @@ tcontb_status finish_run(tcontb_run* run)
         run->umma.tiles_n = u.tiles_n;
         run->umma.raster_group = u.raster_group;
         run->umma.C = static_cast<float*>(run->dC);
+        run->umma.C64 = static_cast<double*>(run->dC);
         run->umma.status = static_cast<int*>(run->status.ptr);
         run->umma.prof = nullptr;
         if (const char* pe = std::getenv("TCONT_UMMA_PROF")) {
@@ -237,11 +242,12 @@ tcontb_status finish_run(tcontb_run* run)
                 run->umma.prof = static_cast<long long*>(run->prof.ptr);
             }
         }
-        tcontb_status st = encode_map(u.a, kA, &run->tmA);
+        tcontb_status st = encode_map(u.a, kA, u.elt, &run->tmA);
         if (st != TCONTB_OK) return st;
-        st = encode_map(u.b, kB, &run->tmB);
+        st = encode_map(u.b, kB, u.elt, &run->tmB);
         if (st != TCONTB_OK) return st;
-        TC_CUDA(umma_tf32_configure(u.smem_bytes));
+        if (pl.kernel == KERNEL_UMMA_TF32) TC_CUDA(umma_tf32_configure(u.smem_bytes));
+        else TC_CUDA(dmma_tma_configure(u.smem_bytes));
     } else {
         OffsetTables t;
         build_offset_tables(p, &t);
@@ -606,6 +612,8 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
     if (t) TC_CUDA(cudaEventRecord(run->ev[2], run->stream));
     if (pl.kernel == KERNEL_UMMA_TF32)
         TC_CUDA(launch_umma_tf32(run->umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
+    else if (pl.kernel == KERNEL_DMMA_F64_TMA)
+        TC_CUDA(launch_dmma_tma(run->umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
     else if (pl.kernel == KERNEL_DMMA_F64)
         TC_CUDA(launch_dmma_contract(run->simt, run->num_sms, run->stream));
     else

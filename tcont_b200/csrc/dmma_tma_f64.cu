@@ -1,0 +1,429 @@
+// dmma_tma_f64.cu -- FP64 direct contraction: TMA-staged operand tiles feeding mma.sync m8n8k4.
+//
+// tcgen05 has no FP64 kind, so the arithmetic is warp-level DMMA (37.0 TFLOP/s measured on B200).
+// What the gather kernel (dmma_f64.cu) spends on address arithmetic is done here by the copy
+// engine: the planner's slab machinery, the same as for the tcgen05 kernel but with 16 doubles per
+// 128-byte row, describes every operand tile as a few multi-mode TMA boxes.
+//
+// One block per SM, three warpgroups; setmaxnreg moves the register budget from the first (56 per
+// thread) to the other two (224):
+//   warps 0, 1  producers, one per consumer group: lane i issues copy i of a stage (5-D tensor
+//               maps, 128-byte swizzle, no multicast) into the group's own ring of stages,
+//               full/empty mbarriers per stage, the ring runs across tile boundaries
+//   warps 2, 3  table builders: for every tile, ahead of time, the C offset of each of its 128 rows
+//               and 64 columns (mixed-radix slab arithmetic, the same as the tcgen05 epilogue),
+//               double-buffered per group behind mbarriers
+//   warps 4-7   consumer group 0, warps 8-11 consumer group 1.  A group is 2 x 2 warps with a
+//               64 x 32 warp tile (8 x 4 accumulator fragments) and takes every other tile of the
+//               block.  Group 1 starts half a main loop late, so one group's stores fall into the
+//               other's main loop instead of both storing with the FP64 pipe idle.
+// Fragment rows are permuted so that one 16-byte shared load of an MN-major operand feeds two
+// fragments (rows 2 r and 2 r + 1 of a 16-row slab) without bank conflicts, and the MMA is issued
+// transposed (B fragment as the row operand): a thread then owns four consecutive elements of C's
+// stride-1 mode per fragment pair and a warp store instruction writes eight whole 128-byte lines.
+// The loads of the next k step are issued between the MMAs of the current one.
+// Every wait is bounded and raises the run's status word instead of hanging.
+//
+// Stands where the reference runs its generated FP64 WMMA kernels
+// (backends/cogent/plan/generators/kernels/kernel_compute.py:127-850) and its cublasGemmEx FP64
+// call (backends/ttgt_cutt/src/ttgt_cutt.cpp:764-809).
+#include <cuda.h>
+
+#include "kernels.hpp"
+#include "tile_common.cuh"
+
+namespace tcontb {
+namespace {
+
+constexpr int kThreads64 = 384;
+constexpr int kBM = 128, kBN = 64;
+constexpr uint32_t kTabBytes = (kBM + kBN) * 8u;  // one tile's row and column offsets
+
+__device__ __forceinline__ double ld_shared_f64(uint32_t addr)
+{
+    double v;
+    asm volatile("ld.shared.f64 %0, [%1];" : "=d"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void ld_shared_v2f64(uint32_t addr, double& x, double& y)
+{
+    asm volatile("ld.shared.v2.f64 {%0, %1}, [%2];" : "=d"(x), "=d"(y) : "r"(addr));
+}
+
+__device__ __forceinline__ void dmma_m8n8k4(double (&c)[2], double a, double b)
+{
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
+                 : "+d"(c[0]), "+d"(c[1])
+                 : "d"(a), "d"(b));
+}
+
+__device__ __forceinline__ void st_global_cs_v4f64(double* p, double a, double b, double c, double d)
+{
+    asm volatile("st.global.cs.v4.f64 [%0], {%1, %2, %3, %4};" ::"l"(p), "d"(a), "d"(b), "d"(c), "d"(d) : "memory");
+}
+
+// Where a thread finds its fragments of one operand for one k (k = k4 + lane % 4):
+//   MN-major (rows of the stage are k, 16 consecutive m per row, slabs of 16 m `pitch` apart):
+//     one 16-byte load at  q0 + pair * pitch  holds fragments 2 pair and 2 pair + 1
+//   K-major (rows of the stage are m, 16 consecutive k per row):
+//     fragment i at  (i odd ? q1 : q0) + (i / 2) * 2048
+// Either way the 16-byte chunk index inside a 128-byte row is XORed with (row % 8).
+struct FragAddr {
+    uint32_t q0, q1;
+};
+
+template <bool MN>
+__device__ __forceinline__ FragAddr frag_addr(uint32_t thread_base, uint32_t k, uint32_t fr)
+{
+    FragAddr f;
+    if (MN) {
+        f.q0 = thread_base + k * 128u + ((fr ^ (k & 7u)) << 4);
+        f.q1 = 0;
+    } else {
+        const uint32_t kk = (k & 1u) * 8u, kc = k >> 1;
+        f.q0 = thread_base + kk + ((kc ^ ((2u * fr) & 7u)) << 4);
+        f.q1 = thread_base + 128u + kk + ((kc ^ ((2u * fr + 1u) & 7u)) << 4);
+    }
+    return f;
+}
+
+// load `n` fragments (n = 8 for A, 4 for B), all at once
+template <bool MN, int N>
+__device__ __forceinline__ void load_all(double (&f)[N], const FragAddr& q, uint32_t pitch)
+{
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        if (MN) {
+            if ((i & 1) == 0) ld_shared_v2f64(q.q0 + static_cast<uint32_t>(i >> 1) * pitch, f[i], f[i + 1]);
+        } else {
+            f[i] = ld_shared_f64(((i & 1) ? q.q1 : q.q0) + static_cast<uint32_t>(i >> 1) * 2048u);
+        }
+    }
+}
+
+// One k4 step of a warp: 32 MMAs on the current fragments; with PF the fragment loads of the next
+// step are issued between them, where the FP64 tensor pipe leaves issue slots free.
+// acc[i][j][h]: row m = 16 (i / 2) + 4 (lane % 4) + 2 h + (i % 2), column n = 16 (j / 2) + 2 (lane / 4) + (j % 2).
+template <bool PF, bool AMN, bool BMN>
+__device__ __forceinline__ void mma_step(double (&acc)[8][4][2], const double (&ac)[8], const double (&bc)[4], double (&an)[8],
+                                         double (&bn)[4], const FragAddr& qa, const FragAddr& qb, uint32_t a_pitch, uint32_t b_pitch)
+{
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dmma_m8n8k4(acc[i][j], bc[j], ac[i]);
+        if (PF) {
+            if (AMN) {
+                if ((i & 1) == 0) ld_shared_v2f64(qa.q0 + static_cast<uint32_t>(i >> 1) * a_pitch, an[i], an[i + 1]);
+            } else {
+                an[i] = ld_shared_f64(((i & 1) ? qa.q1 : qa.q0) + static_cast<uint32_t>(i >> 1) * 2048u);
+            }
+            if (BMN) {
+                if (i == 1 || i == 3) ld_shared_v2f64(qb.q0 + static_cast<uint32_t>(i >> 1) * b_pitch, bn[i - 1], bn[i]);
+            } else {
+                if (i < 4) bn[i] = ld_shared_f64(((i & 1) ? qb.q1 : qb.q0) + static_cast<uint32_t>(i >> 1) * 2048u);
+            }
+        }
+    }
+}
+
+template <bool AMN, bool BMN>
+__global__ void __launch_bounds__(kThreads64, 1)
+dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+                const __grid_constant__ UmmaParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // 1024-byte aligned
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int SA = p.a.slabs_per_tile, SB = p.b.slabs_per_tile;
+    const uint32_t a_tile_bytes = static_cast<uint32_t>(SA * p.a.slab_bytes);
+    const uint32_t stage_bytes = a_tile_bytes + static_cast<uint32_t>(SB * p.b.slab_bytes);
+
+    uint8_t* aux = smem + static_cast<size_t>(p.stages) * stage_bytes;
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(aux);  // [8]
+    uint64_t* bar_empty = bar_full + 8;                     // [8]
+    const uint32_t abort_flag = smem_u32(bar_empty + 8);
+    uint64_t* tab_full = bar_empty + 10;   // [group][buffer]
+    uint64_t* tab_empty = tab_full + 4;    // [group][buffer]
+    const uint32_t tabs = smem_u32(aux + 256);  // [group][buffer]: long long [128] row offsets, [64] column offsets (-1 = beyond C)
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(bar_full + s), 1);
+            mbar_init(smem_u32(bar_empty + s), 4);  // one arrival per consumer warp
+        }
+        for (int s = 0; s < 4; ++s) {
+            mbar_init(smem_u32(tab_full + s), 64);  // every builder thread
+            mbar_init(smem_u32(tab_empty + s), 4);  // one arrival per consumer warp
+        }
+        st_shared_u32(abort_flag, 0u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    const uint32_t tiles_m = static_cast<uint32_t>(p.tiles_m), tiles_n = static_cast<uint32_t>(p.tiles_n);
+    const uint32_t total_tiles = tiles_m * tiles_n;
+    const uint32_t my_tiles = blockIdx.x < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t k_iters = static_cast<uint32_t>(p.k_iters);
+    const uint32_t ring = static_cast<uint32_t>(p.stages) / 2u;  // stages per group
+
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp < 2) {
+            // ---------------- TMA producer of group `warp`: lane i owns copy i of the stage ----------------
+            const uint32_t first = static_cast<uint32_t>(warp) * ring;  // first stage of this group's ring
+            const int OA = SA / p.a.slabs_per_op, OB = SB / p.b.slabs_per_op;
+            const bool is_a = lane < OA;
+            const bool active = lane < OA + OB;
+            const UmmaOperandDev& o = is_a ? p.a : p.b;
+            const void* tmap = is_a ? static_cast<const void*>(&tmapA) : static_cast<const void*>(&tmapB);
+            const int slab = is_a ? lane * p.a.slabs_per_op : (lane - OA) * p.b.slabs_per_op;
+            const uint32_t my_off = is_a ? static_cast<uint32_t>(slab * p.a.slab_bytes)
+                                         : a_tile_bytes + static_cast<uint32_t>(slab * p.b.slab_bytes);
+            if (lane == 0) {
+                asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmapA)) : "memory");
+                asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmapB)) : "memory");
+            }
+            uint32_t stage = 0, phase = 0;
+            uint32_t issued_mask = 0, issued_parity = 0;
+            for (uint32_t i = static_cast<uint32_t>(warp); i < my_tiles; i += 2) {
+                const uint32_t tile = blockIdx.x + i * gridDim.x;
+                uint32_t tm, tn;
+                decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &tm, &tn);
+                int base[kMaxTmaRank] = {0, 0, 0, 0, 0};
+                if (active) {
+                    const uint32_t s = (is_a ? tm * SA : tn * SB) + slab;
+                    if (s < static_cast<uint32_t>(o.total_slabs)) {
+                        uint32_t rem = s;
+    #pragma unroll
+                        for (int d = 0; d < kMaxTmaRank; ++d) {
+                            if (d < o.n_row_digits) {
+                                const uint32_t e = static_cast<uint32_t>(o.row_digit_ext[d]);
+                                const int idx = static_cast<int>(rem % e);
+                                rem /= e;
+                                const int v = d == 0 ? idx * o.digit0_scale : idx;
+    #pragma unroll
+                                for (int t = 0; t < kMaxTmaRank; ++t)
+                                    if (o.row_digit_dim[d] == t) base[t] = v;
+                            }
+                        }
+                    } else {
+                        // Slab beyond the tensor: start the box past the slab mode's end, TMA fills zeros.
+    #pragma unroll
+                        for (int t = 0; t < kMaxTmaRank; ++t)
+                            if (o.row_digit_dim[0] == t) base[t] = o.oob_coord;
+                    }
+                }
+                int kd0 = 0, kd1 = 0, kd2 = 0;
+                for (uint32_t it = 0; it < k_iters; ++it) {
+                    const uint32_t ps = first + stage;
+                    const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + ps), phase ^ 1u, abort_flag));
+                    if (ok) {
+                        if (lane == 0) mbar_arrive_expect_tx(smem_u32(bar_full + ps), stage_bytes);
+                        __syncwarp();
+                        if (active) {
+                            int c[kMaxTmaRank];
+    #pragma unroll
+                            for (int t = 0; t < kMaxTmaRank; ++t) {
+                                c[t] = base[t];
+                                if (o.k_digit_dim[0] == t) c[t] = kd0 * p.BK;
+                                if (o.k_digit_dim[1] == t) c[t] = kd1;
+                                if (o.k_digit_dim[2] == t) c[t] = kd2;
+                            }
+                            tma_load_5d(smem_u32(smem + static_cast<size_t>(ps) * stage_bytes + my_off), tmap,
+                                        smem_u32(bar_full + ps), c[0], c[1], c[2], c[3], c[4]);
+                        }
+                        issued_mask |= 1u << ps;
+                        issued_parity = (issued_parity & ~(1u << ps)) | (phase << ps);
+                    }
+                    if (++kd0 == p.k_digit_ext[0]) {
+                        kd0 = 0;
+                        if (++kd1 == p.k_digit_ext[1]) {
+                            kd1 = 0;
+                            ++kd2;
+                        }
+                    }
+                    if (++stage == ring) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (ld_shared_u32(abort_flag) && lane == 0) {
+                // Give the bulk copies issued into these barriers a bounded time to land before the block ends.
+                for (int s = 0; s < p.stages; ++s) {
+                    if (!(issued_mask & (1u << s))) continue;
+                    const unsigned long long t0 = global_timer();
+                    while (!mbar_try_wait(smem_u32(bar_full + s), (issued_parity >> s) & 1u))
+                        if (global_timer() - t0 > 100000000ull) break;
+                }
+            }
+        } else {
+            // ---------------- table builders: 64 threads, three entries each per tile ----------------
+            const int bt = threadIdx.x - 64;
+            for (uint32_t i = 0; i < my_tiles; ++i) {
+                const uint32_t tile = blockIdx.x + i * gridDim.x;
+                uint32_t tm, tn;
+                decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &tm, &tn);
+                const uint32_t slot = (i & 1u) * 2u + ((i >> 1) & 1u);  // group, buffer
+                const uint32_t use = i >> 2;                            // how often this slot was filled before
+                if (!mbar_wait(smem_u32(tab_empty + slot), (use & 1u) ^ 1u, abort_flag)) break;
+                const uint32_t tab = tabs + slot * kTabBytes;
+#pragma unroll
+                for (int e3 = 0; e3 < 3; ++e3) {
+                    const int e = bt + e3 * 64;
+                    const bool is_row = e < kBM;
+                    const UmmaOperandDev& o = is_row ? p.a : p.b;
+                    const int idx = is_row ? e : e - kBM;
+                    const int sl = idx / o.slab_w, in = idx % o.slab_w;
+                    bool ok;
+                    int d0 = 0;
+                    const long long off = slab_c_offset(o, (is_row ? tm * SA : tn * SB) + sl, &d0, &ok);
+                    ok = ok && (d0 * o.slab_w + in < o.slab_mode_ext);
+                    st_shared_s64(tab + static_cast<uint32_t>(e) * 8u, ok ? off + in * o.row_elem_cstride : -1);
+                }
+                mbar_arrive(smem_u32(tab_full + slot));
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        // ---------------- consumers: two groups of 2 x 2 warps, warp tile 64 x 32 ----------------
+        const int cw = warp & 3, grp = (warp >> 2) - 1, wm = cw & 1, wn = cw >> 1;
+        const uint32_t fr = static_cast<uint32_t>(lane >> 2), fk = static_cast<uint32_t>(lane & 3);
+        double* __restrict__ C = p.C64;
+        const uint32_t first = static_cast<uint32_t>(grp) * ring;
+        const uint32_t a_pitch = static_cast<uint32_t>(p.a.slab_bytes), b_pitch = static_cast<uint32_t>(p.b.slab_bytes);
+        const uint32_t a_thread = AMN ? static_cast<uint32_t>(wm * 4) * a_pitch : (static_cast<uint32_t>(wm * 64) + 2u * fr) * 128u;
+        const uint32_t b_thread = a_tile_bytes + (BMN ? static_cast<uint32_t>(wn * 2) * b_pitch : (static_cast<uint32_t>(wn * 32) + 2u * fr) * 128u);
+
+        double acc[8][4][2];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+        uint32_t stage = 0, phase = 0;
+        const bool prof = p.prof != nullptr && (threadIdx.x & 127) == 0 && grp == 0;
+        long long t_all = prof ? clock64() : 0, t_full = 0, t_main = 0, t_tab = 0, t_store = 0;
+
+        for (uint32_t i = static_cast<uint32_t>(grp); i < my_tiles; i += 2) {
+            long long t0 = prof ? clock64() : 0;
+            // group 1 starts half a main loop behind group 0 (named barrier 1: 128 waiting, 128 arriving)
+            if (i == 1) asm volatile("bar.sync 1, 256;" ::: "memory");
+
+            bool tile_ok = true;
+            for (uint32_t it = 0; it < k_iters; ++it) {
+                if (i == 0 && my_tiles > 1 && it == k_iters / 2) asm volatile("bar.arrive 1, 256;" ::: "memory");
+                const uint32_t ps = first + stage;
+                const long long tw = prof ? clock64() : 0;
+                const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_full + ps), phase, abort_flag));
+                if (prof) t_full += clock64() - tw;
+                tile_ok = tile_ok && ok;
+                if (ok) {
+                    const uint32_t sb = smem_u32(smem) + ps * stage_bytes;
+                    double fa0[8], fb0[4], fa1[8], fb1[4];
+                    FragAddr qa = frag_addr<AMN>(sb + a_thread, fk, fr), qb = frag_addr<BMN>(sb + b_thread, fk, fr);
+                    load_all<AMN, 8>(fa0, qa, a_pitch);
+                    load_all<BMN, 4>(fb0, qb, b_pitch);
+                    qa = frag_addr<AMN>(sb + a_thread, 4u + fk, fr), qb = frag_addr<BMN>(sb + b_thread, 4u + fk, fr);
+                    mma_step<true, AMN, BMN>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
+                    if (p.BK == 16) {
+                        qa = frag_addr<AMN>(sb + a_thread, 8u + fk, fr), qb = frag_addr<BMN>(sb + b_thread, 8u + fk, fr);
+                        mma_step<true, AMN, BMN>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
+                        qa = frag_addr<AMN>(sb + a_thread, 12u + fk, fr), qb = frag_addr<BMN>(sb + b_thread, 12u + fk, fr);
+                        mma_step<true, AMN, BMN>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
+                    }
+                    mma_step<false, AMN, BMN>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(bar_empty + ps));  // this warp is done reading the stage
+                if (++stage == ring) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (prof) { const long long t1 = clock64(); t_main += t1 - t0; t0 = t1; }
+
+            // the tile's offset tables were built while it was being computed
+            const uint32_t slot = static_cast<uint32_t>(grp) * 2u + ((i >> 1) & 1u);
+            tile_ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(tab_full + slot), (i >> 2) & 1u, abort_flag)) && tile_ok;
+            const uint32_t row_tab = tabs + slot * kTabBytes, col_tab = row_tab + kBM * 8u;
+            if (prof) { const long long t1 = clock64(); t_tab += t1 - t0; t0 = t1; }
+
+            // store: four consecutive rows per (fragment pair, column fragment), 32 bytes when aligned
+            long long cn[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                cn[j] = ld_shared_s64(col_tab + (static_cast<uint32_t>(wn * 32 + 16 * (j >> 1) + (j & 1)) + 2u * fr) * 8u);
+#pragma unroll
+            for (int pr = 0; pr < 4; ++pr) {
+                const uint32_t r = static_cast<uint32_t>(wm * 64 + 16 * pr) + 4u * fk;
+                const long long cm0 = ld_shared_s64(row_tab + r * 8u), cm1 = ld_shared_s64(row_tab + r * 8u + 8u);
+                const long long cm2 = ld_shared_s64(row_tab + r * 8u + 16u), cm3 = ld_shared_s64(row_tab + r * 8u + 24u);
+                const bool run4 = cm0 >= 0 && cm1 == cm0 + 1 && cm2 == cm0 + 2 && cm3 == cm0 + 3;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (tile_ok && cn[j] >= 0) {
+                        double* dst = C + cm0 + cn[j];
+                        if (run4 && (reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
+                            st_global_cs_v4f64(dst, acc[2 * pr][j][0], acc[2 * pr + 1][j][0], acc[2 * pr][j][1], acc[2 * pr + 1][j][1]);
+                        } else {
+                            if (cm0 >= 0) __stcs(C + cm0 + cn[j], acc[2 * pr][j][0]);
+                            if (cm1 >= 0) __stcs(C + cm1 + cn[j], acc[2 * pr + 1][j][0]);
+                            if (cm2 >= 0) __stcs(C + cm2 + cn[j], acc[2 * pr][j][1]);
+                            if (cm3 >= 0) __stcs(C + cm3 + cn[j], acc[2 * pr + 1][j][1]);
+                        }
+                    }
+                    acc[2 * pr][j][0] = acc[2 * pr][j][1] = acc[2 * pr + 1][j][0] = acc[2 * pr + 1][j][1] = 0.0;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(tab_empty + slot));  // this warp is done with the tables
+            if (prof) t_store += clock64() - t0;
+        }
+        if (prof) {
+            long long* q = p.prof + static_cast<size_t>(blockIdx.x) * 8;
+            q[0] = clock64() - t_all;
+            q[1] = t_full;
+            q[2] = t_main;
+            q[3] = t_tab;
+            q[4] = t_store;
+            q[5] = 0;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && ld_shared_u32(abort_flag)) atomicMax(p.status, 1);
+}
+
+template <bool AMN, bool BMN>
+cudaError_t launch_variant(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, unsigned grid, cudaStream_t stream)
+{
+    dmma_tma_kernel<AMN, BMN><<<grid, kThreads64, smem_bytes, stream>>>(*static_cast<const CUtensorMap*>(tmapA),
+                                                                         *static_cast<const CUtensorMap*>(tmapB), p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t dmma_tma_configure(int smem_bytes)
+{
+    cudaError_t e = cudaFuncSetAttribute(dmma_tma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    return e;
+}
+
+cudaError_t launch_dmma_tma(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms, cudaStream_t stream)
+{
+    const long long total = p.tiles_m * p.tiles_n;
+    if (total <= 0 || p.stages < 2 || (p.stages & 1)) return cudaErrorInvalidValue;
+    const unsigned grid = static_cast<unsigned>(total < num_sms ? total : num_sms);
+    if (p.a.major && p.b.major) return launch_variant<true, true>(p, tmapA, tmapB, smem_bytes, grid, stream);
+    if (p.a.major) return launch_variant<true, false>(p, tmapA, tmapB, smem_bytes, grid, stream);
+    if (p.b.major) return launch_variant<false, true>(p, tmapA, tmapB, smem_bytes, grid, stream);
+    return launch_variant<false, false>(p, tmapA, tmapB, smem_bytes, grid, stream);
+}
+
+}  // namespace tcontb

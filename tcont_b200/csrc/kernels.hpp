@@ -61,7 +61,8 @@ struct UmmaParams {
     int k_iters;
     long long tiles_m, tiles_n;
     int raster_group;
-    float* C;
+    float* C;       // tcgen05 TF32 kernel
+    double* C64;    // TMA-fed FP64 kernel
     int* status;  // device status word: set non-zero when a bounded wait gives up
     long long* prof;  // optional per-CTA cycle counters [grid][8] (TCONT_UMMA_PROF=1), else null
 };
@@ -69,5 +70,10 @@ struct UmmaParams {
 cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,
                              cudaStream_t stream);
 cudaError_t umma_tf32_configure(int smem_bytes);
+
+// ---- TMA-fed FP64 tensor-path contraction (dmma_tma_f64.cu), same parameter block ------------
+cudaError_t launch_dmma_tma(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,
+                            cudaStream_t stream);
+cudaError_t dmma_tma_configure(int smem_bytes);
 
 }  // namespace tcontb

@@ -162,6 +162,7 @@ int build_problem(const std::string& mC, const std::string& mL, const std::strin
 bool stage_operand(const Problem& p, const std::vector<int>& t, const std::vector<int>& rows, bool is_a, int kc_mode,
                    int BK, UmmaOperand* o, std::string* why)
 {
+    const int elt = p.scalar_type == 1 ? 8 : 4, W = 128 / elt;  // W = elements per 128-byte swizzle row
     o->rank = static_cast<int>(t.size());
     for (int d = 0; d < kMaxTmaRank; ++d) {
         o->ext[d] = 1;
@@ -180,11 +181,11 @@ bool stage_operand(const Problem& p, const std::vector<int>& t, const std::vecto
         }
     }
     for (int d = o->rank; d < kMaxTmaRank; ++d) o->stride[d] = s;  // padded unit dims
-    if (s * 4 >= (int64_t(1) << 40)) {
+    if (s * elt >= (int64_t(1) << 40)) {
         *why = "tensor too large for TMA strides";
         return false;
     }
-    if (o->rank >= 2 && (o->ext[0] % 4) != 0) {
+    if (o->rank >= 2 && (o->ext[0] % (16 / elt)) != 0) {
         *why = "stride-1 extent is not a multiple of 16 bytes (TMA global strides)";
         return false;
     }
@@ -194,7 +195,7 @@ bool stage_operand(const Problem& p, const std::vector<int>& t, const std::vecto
     int slab_mode;
     if (o->major == 1) {
         slab_mode = first;
-        o->slab_w = 32;
+        o->slab_w = W;
     } else {
         if (first != kc_mode) {
             *why = "K-major operand whose stride-1 mode is not the chunked K mode";
@@ -215,6 +216,7 @@ bool stage_operand(const Problem& p, const std::vector<int>& t, const std::vecto
 void finish_operand(const Problem& p, const std::vector<int>& t, const std::vector<int>& rows, int tile_rows, int BK,
                     const std::vector<int>& kdigits, UmmaOperand* o, int max_slab_rows = 256)
 {
+    const int W = p.scalar_type == 1 ? 16 : 32;
     if (o->major == 0) {
         // K-major: rows per slab = the largest power of two (8..tile height) that pads the slab
         // mode by at most 15 %; failing that, the one that pads least.
@@ -251,17 +253,17 @@ void finish_operand(const Problem& p, const std::vector<int>& t, const std::vect
     for (int i = 0; i < 3; ++i)
         o->k_digit_dim[i] = i < static_cast<int>(kdigits.size()) ? index_of(t, kdigits[static_cast<size_t>(i)]) : -1;
     if (o->major == 1) {
-        o->box[o->slab_dim] = 32;
+        o->box[o->slab_dim] = W;
         o->box[o->kc_dim] = BK;
         o->slab_bytes = BK * 128;
     } else {
-        o->box[o->kc_dim] = 32;
+        o->box[o->kc_dim] = W;
         o->box[o->slab_dim] = o->slab_w;
         o->slab_bytes = o->slab_w * 128;
     }
     o->slabs_per_op = 1;
     o->digit0_scale = o->slab_w;
-    o->oob_coord = static_cast<int>(ceil_div(o->slab_mode_ext, 32) * 32);
+    o->oob_coord = static_cast<int>(ceil_div(o->slab_mode_ext, W) * W);
 }
 
 // Merged boxes for an MN-major operand: the slab mode (stride-1, extent a multiple of 32) is
@@ -272,17 +274,18 @@ void finish_operand(const Problem& p, const std::vector<int>& t, const std::vect
 // against 615 with 2).  `cta_slabs` = slabs of this operand one CTA stages per K step.
 void merge_slabs(UmmaOperand* o, int BK, int cta_slabs)
 {
-    if (o->major != 1 || o->rank > kMaxTmaRank - 1 || o->slab_dim != 0 || o->slab_mode_ext % 32) return;
-    const int64_t chunks = o->slab_mode_ext / 32;
+    const int W = o->slab_w;  // 32 floats or 16 doubles
+    if (o->major != 1 || o->rank > kMaxTmaRank - 1 || o->slab_dim != 0 || o->slab_mode_ext % W) return;
+    const int64_t chunks = o->slab_mode_ext / W;
     int g = 1;
     while (g * 2 <= cta_slabs && chunks % (g * 2) == 0 && cta_slabs % (g * 2) == 0) g *= 2;
     if (g <= 1) return;
     UmmaOperand n = *o;
     int map[kMaxTmaRank];
     for (int d = 0; d < kMaxTmaRank; ++d) map[d] = -1;
-    n.ext[0] = 32; n.stride[0] = 1;
+    n.ext[0] = W; n.stride[0] = 1;
     n.ext[1] = o->ext[o->kc_dim]; n.stride[1] = o->stride[o->kc_dim];
-    n.ext[2] = chunks; n.stride[2] = 32;
+    n.ext[2] = chunks; n.stride[2] = W;
     map[0] = 2;
     map[o->kc_dim] = 1;
     int next = 3;
@@ -296,7 +299,7 @@ void merge_slabs(UmmaOperand* o, int BK, int cta_slabs)
     for (int d = next; d < kMaxTmaRank; ++d) { n.ext[d] = 1; n.stride[d] = total; }
     n.rank = o->rank + 1;
     for (int d = 0; d < kMaxTmaRank; ++d) n.box[d] = 1;
-    n.box[0] = 32; n.box[1] = BK; n.box[2] = g;
+    n.box[0] = W; n.box[1] = BK; n.box[2] = g;
     n.slab_dim = 2;
     n.kc_dim = 1;
     for (int i = 0; i < o->n_row_digits; ++i) n.row_digit_dim[i] = map[o->row_digit_dim[i]];
@@ -310,8 +313,12 @@ void merge_slabs(UmmaOperand* o, int BK, int cta_slabs)
 void plan_umma(const Problem& p, UmmaSpec* u)
 {
     u->eligible = false;
-    if (p.scalar_type != 0) { u->why_not = "not Float32"; return; }
+    const bool f64 = p.scalar_type == 1;
+    const int elt = f64 ? 8 : 4, W = 128 / elt;
+    u->elt = elt;
     if (const char* k = std::getenv("TCONT_KERNEL")) {
+        // Debug switch: TCONT_KERNEL=gather keeps FP64 on the cp.async gather kernel.
+        if (f64 && std::strcmp(k, "gather") == 0) { u->why_not = "disabled by TCONT_KERNEL=gather"; return; }
         // Debug switch: TCONT_KERNEL=simt keeps Float32 contractions on the CUDA-core kernel.
         if (std::strcmp(k, "simt") == 0) { u->why_not = "disabled by TCONT_KERNEL=simt"; return; }
     }
@@ -355,8 +362,8 @@ void plan_umma(const Problem& p, UmmaSpec* u)
     }
     const int64_t kc_ext = p.modes[static_cast<size_t>(kc)].extent;
     u->kc_names = p.modes[static_cast<size_t>(kc)].names;
-    int BK = 32;
-    if (!a_kmajor && !b_kmajor) BK = kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32;
+    int BK = W;  // a K-major operand brings 128 bytes of K per row
+    if (!a_kmajor && !b_kmajor) BK = f64 ? (kc_ext <= 8 ? 8 : 16) : (kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32);
     u->BK = BK;
     std::vector<int> kdigits{kc};
     for (int id : p.K)
@@ -378,7 +385,9 @@ void plan_umma(const Problem& p, UmmaSpec* u)
     // N tile: the widest of 256/128/64/32 that is not wider than the (padded) N extent needs and
     // still yields at least one tile per SM; otherwise the narrowest admissible one.
     int bn = 32;
-    {
+    if (f64) {
+        bn = 64;  // the FP64 kernel has one tile shape: 128 x 64
+    } else {
         UmmaOperand probe = u->b;
         finish_operand(p, p.B, p.N, 32, BK, kdigits, &probe);
         const int64_t padded = probe.total_slabs * probe.slab_w;
@@ -416,9 +425,10 @@ void plan_umma(const Problem& p, UmmaSpec* u)
         // 605 TFLOP/s; cfg5: 455 vs 526): the MMA of a pair reads half of B from the partner SM and issues
         // more slowly, which eats the saving in copies.  It therefore stays opt-in.
         bool pair = false;
+        if (f64) b2 = u->b;
         if (const char* e = std::getenv("TCONT_UMMA_PAIR")) {
             if (e[0] == '0') pair = false;
-            else if (e[0] == '1') pair = u->tiles_m >= 2 && b2.slabs_per_tile % 2 == 0;
+            else if (e[0] == '1') pair = !f64 && u->tiles_m >= 2 && b2.slabs_per_tile % 2 == 0;
         }
         if (pair) {
             u->pair = true;
@@ -429,8 +439,8 @@ void plan_umma(const Problem& p, UmmaSpec* u)
     {
         const double a_bytes = double(u->a.slabs_per_tile) * u->a.slab_bytes;
         const double b_bytes = double(u->b.slabs_per_tile) * u->b.slab_bytes;
-        const bool a_far = u->a.major == 1 && u->a.stride[u->a.kc_dim] * 4 >= 65536;
-        const bool b_far = u->b.major == 1 && u->b.stride[u->b.kc_dim] * 4 >= 65536;
+        const bool a_far = u->a.major == 1 && u->a.stride[u->a.kc_dim] * elt >= 65536;
+        const bool b_far = u->b.major == 1 && u->b.stride[u->b.kc_dim] * elt >= 65536;
         u->far_fraction = ((a_far ? a_bytes : 0.0) + (b_far ? b_bytes : 0.0)) / (a_bytes + b_bytes);
     }
     if (!std::getenv("TCONT_UMMA_NO_MERGE")) {
@@ -439,8 +449,10 @@ void plan_umma(const Problem& p, UmmaSpec* u)
     }
     const int stage_bytes = u->a.slabs_per_tile * u->a.slab_bytes +
                             (u->pair ? u->b.slabs_per_tile / 2 : u->b.slabs_per_tile) * u->b.slab_bytes;
-    const int budget = 227 * 1024 - 8 * 1024;
+    // both kernels own an SM; the FP64 one stops at eight 24 KB stages
+    const int budget = f64 ? 200 * 1024 : 227 * 1024 - 8 * 1024;
     u->stages = std::max(2, std::min(8, budget / stage_bytes));
+    if (f64) u->stages &= ~1;  // one ring of stages per consumer group
     u->smem_bytes = u->stages * stage_bytes + 8 * 1024 + 1024;
     u->raster_group = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(u->tiles_m,
                       std::llround(std::sqrt(148.0 * u->BN / u->BM)))));
@@ -471,7 +483,15 @@ void fill_transpose(const std::string& src, const std::string& dst, const std::s
 // problems keep the 64 x 64 CUDA-core tiles, which spread over more SMs.
 int pick_kernel(const Problem& p, const UmmaSpec& u)
 {
-    if (u.eligible) return KERNEL_UMMA_TF32;
+    if (u.eligible && u.elt == 4) return KERNEL_UMMA_TF32;
+    // TMA-fed FP64 kernel: needs a tile per SM, rows of C contiguous along the slab mode (its stores are
+    // 64-byte runs per fragment otherwise 8-byte scatters), and a contracted extent long enough to
+    // amortise the per-tile table set-up (measured: cfg3, K = 48, 6.0 ms gathered against 6.6 ms;
+    // K = 312, 25.5 against 20.1 TFLOP/s; 5136^3 GEMM 29.6 against 19.2 TFLOP/s).
+    int64_t min_k = 128;
+    if (const char* e = std::getenv("TCONT_F64_TMA_MIN_K")) min_k = std::atoll(e);
+    if (u.eligible && u.elt == 8 && u.tiles_m * u.tiles_n >= 148 && u.a.row_elem_cstride == 1 && p.Ktot >= min_k)
+        return KERNEL_DMMA_F64_TMA;
     const char* k = std::getenv("TCONT_KERNEL");
     const bool simt_only = k && std::strcmp(k, "simt") == 0;
     const int64_t bn = p.Ntot <= 48 ? 32 : 64, bm = p.Ntot <= 48 ? 256 : 128;  // the tensor-path kernel's smallest fitting tile
@@ -485,7 +505,7 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
     const double flops = 2.0 * double(p.Mtot) * double(p.Ntot) * double(p.Ktot);
     double c_bytes = double(p.sizeC) * elt;
     double rate = p.scalar_type == 1 ? c.simt_f64_tflops : c.simt_f32_tflops;
-    if (kernel == KERNEL_DMMA_F64) rate = c.dmma_f64_tflops;
+    if (kernel == KERNEL_DMMA_F64 || kernel == KERNEL_DMMA_F64_TMA) rate = c.dmma_f64_tflops;
     if (kernel == KERNEL_UMMA_TF32) {
         rate = c.umma_tf32_tflops * (1.0 - c.far_row_penalty * u.far_fraction);
         // rows of a slab that are not contiguous in C cost a 32-byte sector per element
@@ -721,7 +741,8 @@ std::string describe_plan(const Plan& pl)
         return s + "]";
     };
     o << "{\"backend\":\"" << (pl.backend == 0 ? "direct" : "ttgt") << "\",\"kernel\":\""
-      << (pl.kernel == KERNEL_UMMA_TF32 ? "umma_tf32" : pl.kernel == KERNEL_DMMA_F64 ? "dmma_f64" : "simt") << "\""
+      << (pl.kernel == KERNEL_UMMA_TF32 ? "umma_tf32" : pl.kernel == KERNEL_DMMA_F64 ? "dmma_f64"
+          : pl.kernel == KERNEL_DMMA_F64_TMA ? "dmma_f64_tma" : "simt") << "\""
       << ",\"scalar\":\"" << (pl.scalar_type == 1 ? "f64" : "f32") << "\",\"swapped\":" << (p.swapped ? "true" : "false")
       << ",\"A\":" << list(p.A) << ",\"B\":" << list(p.B) << ",\"C\":" << list(p.C) << ",\"M\":" << list(p.M)
       << ",\"N\":" << list(p.N) << ",\"K\":" << list(p.K) << ",\"Mtot\":" << p.Mtot << ",\"Ntot\":" << p.Ntot

@@ -16,7 +16,7 @@ constexpr int kMaxModes = 16;
 constexpr int kMaxTmaRank = 5;
 
 enum ModeGroup { GROUP_M = 0, GROUP_N = 1, GROUP_K = 2 };
-enum KernelKind { KERNEL_SIMT = 0, KERNEL_UMMA_TF32 = 1, KERNEL_DMMA_F64 = 2 };
+enum KernelKind { KERNEL_SIMT = 0, KERNEL_UMMA_TF32 = 1, KERNEL_DMMA_F64 = 2, KERNEL_DMMA_F64_TMA = 3 };
 
 struct Mode {
     std::string names;  // the caller's mode letters fused into this mode, fastest first
@@ -87,6 +87,7 @@ struct UmmaSpec {
     int raster_group = 16;
     bool pair = false;  // two-CTA clusters working on 256-row tiles (tcgen05 cta_group::2)
     int smem_bytes = 0;
+    int elt = 4;  // element bytes: 4 = tcgen05 TF32 kernel, 8 = TMA-fed FP64 tensor-path kernel
 };
 
 struct SimtSpec {

@@ -21,99 +21,12 @@
 #include <cuda.h>
 
 #include "kernels.hpp"
+#include "tile_common.cuh"
 
 namespace tcontb {
 namespace {
 
 constexpr int kThreads = 192;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ unsigned long long global_timer()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-
-// Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit passes, or
-// immediately when another thread of the CTA already gave up.
-__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr)
-{
-    uint32_t v;
-    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v)
-{
-    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ void st_shared_s64(uint32_t addr, long long v)
-{
-    asm volatile("st.shared.b64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
-}
-__device__ __forceinline__ long long ld_shared_s64(uint32_t addr)
-{
-    long long v;
-    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
-    return v;
-}
-
-// Bounded wait.  The fast path is a bare try_wait; every 256 failed polls it looks at the CTA's
-// abort flag (shared-memory word at `abort_addr`) and at the clock.  Returns false, and raises the
-// flag, when the limit passes; returns false at once when another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_addr)
-{
-    unsigned long long t0 = 0;
-    for (uint32_t spin = 0;; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 255u) == 255u || spin == 0) {
-            if (ld_shared_u32(abort_addr)) return false;
-            if (spin == 0) continue;
-            const unsigned long long now = global_timer();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) {
-                st_shared_u32(abort_addr, 1u);
-                return false;
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2, int c3, int c4)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
-        : "memory");
-}
-
 // The same copy for a CTA pair: the destination is this CTA's shared memory, the mbarrier may live
 // in the partner CTA (address in the cluster window).  No multicast.
 __device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0, int c1, int c2, int c3, int c4)
@@ -215,39 +128,6 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Raster order: groups of `g` tile rows are swept column by column, so the CTAs that run
-// together share A and B panels in L2.  Tile and slab counts fit 32 bits (the planner checks).
-__device__ __forceinline__ void decode_tile(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t g, uint32_t* tm, uint32_t* tn)
-{
-    const uint32_t per_group = g * tiles_n;
-    const uint32_t group = tile / per_group;
-    const uint32_t first_m = group * g;
-    const uint32_t rows = (tiles_m - first_m) < g ? (tiles_m - first_m) : g;
-    const uint32_t local = tile - group * per_group;
-    *tm = first_m + local % rows;
-    *tn = local / rows;
-}
-
-// Splits a slab index into its mixed-radix digits and returns the C offset of the slab start.
-// valid = false when the slab lies beyond the tensor.
-__device__ __forceinline__ long long slab_c_offset(const UmmaOperandDev& o, uint32_t slab, int* digit0, bool* valid)
-{
-    *valid = slab < static_cast<uint32_t>(o.total_slabs);
-    uint32_t rem = slab;
-    long long off = 0;
-#pragma unroll
-    for (int d = 0; d < kMaxTmaRank; ++d) {
-        if (d < o.n_row_digits) {
-            const uint32_t e = static_cast<uint32_t>(o.row_digit_ext[d]);
-            const uint32_t idx = rem % e;
-            rem /= e;
-            off += static_cast<long long>(idx) * o.row_digit_cstride[d];
-            if (d == 0) *digit0 = static_cast<int>(idx);
-        }
-    }
-    return off;
-}
 
 // PAIR = false: one CTA per 128 x BN tile (cta_group::1).
 // PAIR = true : a cluster of two CTAs per 256 x BN tile (cta_group::2).  CTA r of the pair stages its own

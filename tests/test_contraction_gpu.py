@@ -89,16 +89,34 @@ def test_tensor_core_shapes(engine, oracle, name):
     check(oracle, c, A, B, out, desc)
 
 
-@pytest.mark.parametrize("c", [
-    Contraction("abcd", "aebf", "fdec", dict(a=50, b=30, c=34, d=50, e=13, f=3), F64),      # ragged in M, N and K
-    Contraction("abcijk", "aeij", "bcek", dict(a=48, b=12, c=12, e=48, i=6, j=6, k=12), F64),  # cfg3's pattern
-    Contraction("ab", "ka", "kb", dict(a=1537, b=1409, k=70), F64),                          # both K-major
-], ids=["ragged4d", "cfg3_like", "kmajor"])
-def test_fp64_tensor_path(engine, oracle, c):
+FP64_SHAPES = {
+    "ragged4d": Contraction("abcd", "aebf", "fdec", dict(a=50, b=30, c=34, d=50, e=13, f=3), F64),      # ragged in M, N and K
+    "cfg3_like": Contraction("abcijk", "aeij", "bcek", dict(a=48, b=12, c=12, e=48, i=6, j=6, k=12), F64),  # cfg3's pattern, short K
+    "kmajor": Contraction("ab", "ka", "kb", dict(a=1537, b=1409, k=70), F64),                          # both K-major, odd extents
+    "gemm_mn_k": Contraction("ab", "ak", "kb", dict(a=1200, b=1000, k=200), F64),                      # MN-major A (merged boxes), K-major B
+    "two_k_long": Contraction("abcd", "aebf", "cfde", dict(a=64, b=40, c=48, d=18, e=24, f=10), F64),  # both MN-major, two K modes
+    "kmajor_long": Contraction("ab", "ka", "kb", dict(a=1537, b=1409, k=262), F64),                   # K-major boxes, ragged everywhere
+    "case21_like": Contraction("abcd", "aebf", "fdec", dict(a=72, b=24, c=24, d=72, e=24, f=16), F64),
+}
+
+
+@pytest.mark.parametrize("name", list(FP64_SHAPES))
+@pytest.mark.parametrize("kernel", ["auto", "gather"])
+def test_fp64_tensor_path(engine, oracle, monkeypatch, name, kernel):
+    """Both FP64 tensor-path kernels: TMA-fed (picked for long contracted extents) and gathered."""
+    if kernel == "gather":
+        monkeypatch.setenv("TCONT_KERNEL", "gather")
+    c = FP64_SHAPES[name]
     A, B = oracle.inputs(c, 31, -1.0, 1.0)
     out, desc = run_contraction(engine, c, A, B, 1)
-    assert desc["kernel"] == "dmma_f64"
+    assert desc["kernel"] in (("dmma_f64",) if kernel == "gather" else ("dmma_f64", "dmma_f64_tma"))
     check(oracle, c, A, B, out, desc)
+
+
+def test_fp64_tma_kernel_is_used_for_long_k(engine):
+    for name in ("gemm_mn_k", "two_k_long", "kmajor_long", "case21_like"):
+        d = engine.plan(to_equation(engine, FP64_SHAPES[name], 1)).describe()
+        assert d["kernel"] == "dmma_f64_tma", (name, d["kernel"], d["umma"])
 
 
 def test_tf32_operands_are_truncated_not_rounded(engine, oracle):
