@@ -19,7 +19,7 @@ OBJ = os.path.join(PKG, "_build")
 LIB_C = os.path.join(PKG, "libtcontb.so")
 LIB_CPP = os.path.join(PKG, "libtcont.so")
 
-CORE_SOURCES = ["planner.cpp", "api.cpp", "simt_contract.cu", "dmma_f64.cu", "dmma_tma_f64.cu", "transpose.cu", "umma_tf32.cu", "no_alloc.cu", "peaks.cu"]
+CORE_SOURCES = ["planner.cpp", "api.cpp", "simt_contract.cu", "dmma_f64.cu", "dmma_tma_f64.cu", "transpose.cu", "umma_tf32.cu", "splitk_reduce.cu", "no_alloc.cu", "peaks.cu"]
 SHIM_SOURCES = ["tcont_shim.cpp"]
 HEADERS = ["planner.hpp", "kernels.hpp", "tile_common.cuh", os.path.join(ROOT, "include", "tcontb.h"), os.path.join(ROOT, "include", "tcont.hpp"),
            os.path.join(ROOT, "include", "tcont_b200", "tcont_api.hpp")]

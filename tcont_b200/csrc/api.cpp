@@ -92,6 +92,7 @@ struct tcontb_run {
     UmmaParams umma{};
     CUtensorMap tmA{}, tmB{};
     DeviceBuffer status;
+    DeviceBuffer splitk;  // partial tensors of a split-K contraction, k_splits copies of C
     DeviceBuffer prof;  // cycle counters of the tcgen05 kernel, only with TCONT_UMMA_PROF=1
     // stage timing
     bool stage_timing = false;
@@ -231,8 +232,17 @@ tcontb_status finish_run(tcontb_run* run)
         run->umma.tiles_m = u.tiles_m;
         run->umma.tiles_n = u.tiles_n;
         run->umma.raster_group = u.raster_group;
-        run->umma.C = static_cast<float*>(run->dC);
-        run->umma.C64 = static_cast<double*>(run->dC);
+        run->umma.k_splits = u.k_splits;
+        run->umma.k_iters_per_split = static_cast<int>(u.k_iters_per_split);
+        run->umma.split_stride = pl.sizeC;
+        void* out = run->dC;
+        if (u.k_splits > 1) {
+            TC_CUDA(run->splitk.alloc(static_cast<size_t>(u.k_splits) * static_cast<size_t>(pl.sizeC) * run->elt));
+            out = run->splitk.ptr;
+            run->kernels_per_launch++;
+        }
+        run->umma.C = static_cast<float*>(out);
+        run->umma.C64 = static_cast<double*>(out);
         run->umma.status = static_cast<int*>(run->status.ptr);
         run->umma.prof = nullptr;
         if (const char* pe = std::getenv("TCONT_UMMA_PROF")) {
@@ -618,6 +628,8 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
         TC_CUDA(launch_dmma_contract(run->simt, run->num_sms, run->stream));
     else
         TC_CUDA(launch_simt_contract(run->simt, pl.scalar_type, run->stream));
+    if (run->splitk.ptr)
+        TC_CUDA(launch_splitk_reduce(run->splitk.ptr, run->dC, pl.sizeC, pl.umma.k_splits, pl.sizeC, static_cast<int>(run->elt), run->stream));
     if (t) {
         TC_CUDA(cudaEventRecord(run->ev[3], run->stream));
         run->ev_valid = true;

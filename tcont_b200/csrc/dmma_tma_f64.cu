@@ -163,9 +163,8 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
     __syncthreads();
 
     const uint32_t tiles_m = static_cast<uint32_t>(p.tiles_m), tiles_n = static_cast<uint32_t>(p.tiles_n);
-    const uint32_t total_tiles = tiles_m * tiles_n;
+    const uint32_t total_tiles = tiles_m * tiles_n * static_cast<uint32_t>(p.k_splits);  // work units (tile, k range)
     const uint32_t my_tiles = blockIdx.x < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const uint32_t k_iters = static_cast<uint32_t>(p.k_iters);
     const uint32_t ring = static_cast<uint32_t>(p.stages) / 2u;  // stages per group
 
     if (warp < 4) {
@@ -188,9 +187,8 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             uint32_t stage = 0, phase = 0;
             uint32_t issued_mask = 0, issued_parity = 0;
             for (uint32_t i = static_cast<uint32_t>(warp); i < my_tiles; i += 2) {
-                const uint32_t tile = blockIdx.x + i * gridDim.x;
-                uint32_t tm, tn;
-                decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &tm, &tn);
+                const WorkUnit w = decode_unit(blockIdx.x + i * gridDim.x, p, tiles_m, tiles_n);
+                const uint32_t tm = w.tm, tn = w.tn;
                 int base[kMaxTmaRank] = {0, 0, 0, 0, 0};
                 if (active) {
                     const uint32_t s = (is_a ? tm * SA : tn * SB) + slab;
@@ -215,8 +213,9 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                             if (o.row_digit_dim[0] == t) base[t] = o.oob_coord;
                     }
                 }
-                int kd0 = 0, kd1 = 0, kd2 = 0;
-                for (uint32_t it = 0; it < k_iters; ++it) {
+                int kd0 = w.it0 % p.k_digit_ext[0], kd1 = (w.it0 / p.k_digit_ext[0]) % p.k_digit_ext[1];
+                int kd2 = w.it0 / (p.k_digit_ext[0] * p.k_digit_ext[1]);
+                for (int it = 0; it < w.n_it; ++it) {
                     const uint32_t ps = first + stage;
                     const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + ps), phase ^ 1u, abort_flag));
                     if (ok) {
@@ -263,9 +262,8 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             // ---------------- table builders: 64 threads, three entries each per tile ----------------
             const int bt = threadIdx.x - 64;
             for (uint32_t i = 0; i < my_tiles; ++i) {
-                const uint32_t tile = blockIdx.x + i * gridDim.x;
-                uint32_t tm, tn;
-                decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &tm, &tn);
+                const WorkUnit w = decode_unit(blockIdx.x + i * gridDim.x, p, tiles_m, tiles_n);
+                const uint32_t tm = w.tm, tn = w.tn;
                 const uint32_t slot = (i & 1u) * 2u + ((i >> 1) & 1u);  // group, buffer
                 const uint32_t use = i >> 2;                            // how often this slot was filled before
                 if (!mbar_wait(smem_u32(tab_empty + slot), (use & 1u) ^ 1u, abort_flag)) break;
@@ -291,7 +289,6 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         // ---------------- consumers: two groups of 2 x 2 warps, warp tile 64 x 32 ----------------
         const int cw = warp & 3, grp = (warp >> 2) - 1, wm = cw & 1, wn = cw >> 1;
         const uint32_t fr = static_cast<uint32_t>(lane >> 2), fk = static_cast<uint32_t>(lane & 3);
-        double* __restrict__ C = p.C64;
         const uint32_t first = static_cast<uint32_t>(grp) * ring;
         const uint32_t a_pitch = static_cast<uint32_t>(p.a.slab_bytes), b_pitch = static_cast<uint32_t>(p.b.slab_bytes);
         const uint32_t a_thread = AMN ? static_cast<uint32_t>(wm * 4) * a_pitch : (static_cast<uint32_t>(wm * 64) + 2u * fr) * 128u;
@@ -312,9 +309,11 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             // group 1 starts half a main loop behind group 0 (named barrier 1: 128 waiting, 128 arriving)
             if (i == 1) asm volatile("bar.sync 1, 256;" ::: "memory");
 
+            const WorkUnit w = decode_unit(blockIdx.x + i * gridDim.x, p, tiles_m, tiles_n);
+            double* __restrict__ C = p.C64 + static_cast<long long>(w.split) * p.split_stride;
             bool tile_ok = true;
-            for (uint32_t it = 0; it < k_iters; ++it) {
-                if (i == 0 && my_tiles > 1 && it == k_iters / 2) asm volatile("bar.arrive 1, 256;" ::: "memory");
+            for (int it = 0; it < w.n_it; ++it) {
+                if (i == 0 && my_tiles > 1 && it == w.n_it / 2) asm volatile("bar.arrive 1, 256;" ::: "memory");
                 const uint32_t ps = first + stage;
                 const long long tw = prof ? clock64() : 0;
                 const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_full + ps), phase, abort_flag));
@@ -417,8 +416,8 @@ cudaError_t dmma_tma_configure(int smem_bytes)
 
 cudaError_t launch_dmma_tma(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms, cudaStream_t stream)
 {
-    const long long total = p.tiles_m * p.tiles_n;
-    if (total <= 0 || p.stages < 2 || (p.stages & 1)) return cudaErrorInvalidValue;
+    const long long total = p.tiles_m * p.tiles_n * p.k_splits;
+    if (total <= 0 || p.k_splits < 1 || p.stages < 2 || (p.stages & 1)) return cudaErrorInvalidValue;
     const unsigned grid = static_cast<unsigned>(total < num_sms ? total : num_sms);
     if (p.a.major && p.b.major) return launch_variant<true, true>(p, tmapA, tmapB, smem_bytes, grid, stream);
     if (p.a.major) return launch_variant<true, false>(p, tmapA, tmapB, smem_bytes, grid, stream);

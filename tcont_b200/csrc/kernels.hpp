@@ -59,6 +59,11 @@ struct UmmaParams {
     int pair;  // 1: two-CTA clusters, 256 x BN tiles (cta_group::2); 0: one CTA per 128 x BN tile
     int k_digit_ext[3];
     int k_iters;
+    // Split-K: every tile is computed k_splits times over consecutive ranges of k_iters_per_split
+    // iterations; split s writes its partial tile at C + s * split_stride (a workspace laid out like
+    // C, summed afterwards by launch_splitk_reduce).  k_splits = 1: the kernel writes C itself.
+    int k_splits, k_iters_per_split;
+    long long split_stride;
     long long tiles_m, tiles_n;
     int raster_group;
     float* C;       // tcgen05 TF32 kernel
@@ -75,5 +80,9 @@ cudaError_t umma_tf32_configure(int smem_bytes);
 cudaError_t launch_dmma_tma(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,
                             cudaStream_t stream);
 cudaError_t dmma_tma_configure(int smem_bytes);
+
+// ---- split-K: C[e] = sum over s of partial[s * stride + e], s ascending (splitk_reduce.cu) ----
+cudaError_t launch_splitk_reduce(const void* partial, void* C, long long elements, int splits, long long stride, int elt_bytes,
+                                 cudaStream_t stream);
 
 }  // namespace tcontb

@@ -454,6 +454,19 @@ void plan_umma(const Problem& p, UmmaSpec* u)
     u->stages = std::max(2, std::min(8, budget / stage_bytes));
     if (f64) u->stages &= ~1;  // one ring of stages per consumer group
     u->smem_bytes = u->stages * stage_bytes + 8 * 1024 + 1024;
+    // Split-K: with clearly less than one wave of tiles and a long contracted extent, cut the k
+    // iterations into ranges computed as separate work units (partials summed by a second kernel).
+    // The FP64 kernel wants two units per SM, one for each of its consumer groups.
+    {
+        const int64_t tiles = (u->pair ? ceil_div(u->tiles_m, 2) : u->tiles_m) * u->tiles_n;
+        const int64_t target = f64 ? 296 : 148;
+        int64_t splits = 1;
+        if (tiles * 4 < target * 3 && u->k_iters >= 8) splits = std::min<int64_t>(ceil_div(target, tiles), u->k_iters / 4);
+        if (const char* e = std::getenv("TCONT_SPLITK")) splits = std::max<int64_t>(1, std::min<int64_t>(std::atoll(e), u->k_iters));
+        while (splits > 1 && double(splits) * double(p.sizeC) * elt > 512.0 * 1024 * 1024) --splits;  // workspace
+        u->k_iters_per_split = ceil_div(u->k_iters, splits);
+        u->k_splits = static_cast<int>(ceil_div(u->k_iters, u->k_iters_per_split));
+    }
     u->raster_group = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(u->tiles_m,
                       std::llround(std::sqrt(148.0 * u->BN / u->BM)))));
     u->eligible = true;
@@ -479,24 +492,24 @@ void fill_transpose(const std::string& src, const std::string& dst, const std::s
     }
 }
 
-// FP64 goes to the tensor-path kernel (128 x 128 tiles) once there is a tile per SM; smaller
-// problems keep the 64 x 64 CUDA-core tiles, which spread over more SMs.
-int pick_kernel(const Problem& p, const UmmaSpec& u)
+// Share of the last wave's SMs that have a tile: t tiles on 148 SMs take ceil(t / 148) rounds.
+double wave_efficiency(int64_t tiles)
 {
-    if (u.eligible && u.elt == 4) return KERNEL_UMMA_TF32;
-    // TMA-fed FP64 kernel: needs a tile per SM, rows of C contiguous along the slab mode (its stores are
-    // 64-byte runs per fragment otherwise 8-byte scatters), and a contracted extent long enough to
-    // amortise the per-tile table set-up (measured: cfg3, K = 48, 6.0 ms gathered against 6.6 ms;
-    // K = 312, 25.5 against 20.1 TFLOP/s; 5136^3 GEMM 29.6 against 19.2 TFLOP/s).
-    int64_t min_k = 128;
-    if (const char* e = std::getenv("TCONT_F64_TMA_MIN_K")) min_k = std::atoll(e);
-    if (u.eligible && u.elt == 8 && u.tiles_m * u.tiles_n >= 148 && u.a.row_elem_cstride == 1 && p.Ktot >= min_k)
-        return KERNEL_DMMA_F64_TMA;
-    const char* k = std::getenv("TCONT_KERNEL");
-    const bool simt_only = k && std::strcmp(k, "simt") == 0;
-    const int64_t bn = p.Ntot <= 48 ? 32 : 64, bm = p.Ntot <= 48 ? 256 : 128;  // the tensor-path kernel's smallest fitting tile
-    if (p.scalar_type == 1 && !simt_only && ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn) >= 148) return KERNEL_DMMA_F64;
-    return KERNEL_SIMT;
+    const int64_t t = std::max<int64_t>(tiles, 1);
+    return double(t) / double(ceil_div(t, 148) * 148);
+}
+
+// The gather kernel fetches 16 bytes per load when the stride-1 mode of an operand is the first row
+// mode of its tile (C's order) or the first contracted mode, and has an even extent; else 8 bytes.
+bool gathers_16_bytes(const Problem& p)
+{
+    auto ok = [&](const std::vector<int>& t, const std::vector<int>& rows) {
+        if (t.empty()) return false;
+        const Mode& m = p.modes[static_cast<size_t>(t[0])];
+        const bool lead = (!rows.empty() && t[0] == rows[0]) || (!p.K.empty() && t[0] == p.K[0]);
+        return lead && m.extent % 2 == 0;
+    };
+    return ok(p.A, p.M) && ok(p.B, p.N);
 }
 
 double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const CostTable& c)
@@ -505,14 +518,64 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
     const double flops = 2.0 * double(p.Mtot) * double(p.Ntot) * double(p.Ktot);
     double c_bytes = double(p.sizeC) * elt;
     double rate = p.scalar_type == 1 ? c.simt_f64_tflops : c.simt_f32_tflops;
-    if (kernel == KERNEL_DMMA_F64 || kernel == KERNEL_DMMA_F64_TMA) rate = c.dmma_f64_tflops;
+    double extra_us = 0;
+    // tiles are computed whole: the work of an FP64 kernel is that of the extents rounded up to its tile
+    auto padded = [&](int64_t bm, int64_t bn) {
+        return double(ceil_div(p.Mtot, bm) * bm) / double(p.Mtot) * double(ceil_div(p.Ntot, bn) * bn) / double(p.Ntot);
+    };
+    if (kernel == KERNEL_SIMT && p.scalar_type == 1)
+        rate *= wave_efficiency(ceil_div(p.Mtot, 64) * ceil_div(p.Ntot, 64)) / padded(64, 64);
+    if ((kernel == KERNEL_DMMA_F64_TMA || kernel == KERNEL_UMMA_TF32) && u.k_splits > 1) {
+        // partial tensors written, read back and summed by a second kernel
+        extra_us += c.launch_us + 2.0 * double(u.k_splits) * double(p.sizeC) * elt / (c.hbm_gbs * 1e3);
+    }
+    if (kernel == KERNEL_DMMA_F64_TMA) {
+        rate = c.dmma_f64_tflops * wave_efficiency(u.tiles_m * u.tiles_n * u.k_splits) / padded(u.BM, u.BN);
+        // Rows of a slab that are not contiguous in C are stored element by element
+        // (abcdef-dega-gfbc: 37.7 M elements of C, 1.08 ms against 0.10 ms for its coalesced siblings).
+        if (u.a.row_elem_cstride != 1) extra_us += double(p.sizeC) * double(u.k_splits) * c.scatter_store_ps * 1e-6;
+    }
+    if (kernel == KERNEL_DMMA_F64) {
+        const int64_t bn = p.Ntot <= 48 ? 32 : 64, bm = p.Ntot <= 48 ? 256 : 128;
+        // Measured: 19 to 20 TFLOP/s with 16-byte gathers on both operands (abc-ad-bdc), 13 to 15 with
+        // one operand on 8-byte gathers (abcd-eafb-fdec), 3.5 to 4.4 on the 256 x 32 tiles for narrow N.
+        const double r = p.Ntot <= 48 ? c.dmma_f64_gather_narrow_tflops
+                                      : (gathers_16_bytes(p) ? c.dmma_f64_gather_tflops : c.dmma_f64_gather8_tflops);
+        rate = r *
+               wave_efficiency(ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn)) / padded(bm, bn);
+    }
     if (kernel == KERNEL_UMMA_TF32) {
-        rate = c.umma_tf32_tflops * (1.0 - c.far_row_penalty * u.far_fraction);
+        rate = c.umma_tf32_tflops * (1.0 - c.far_row_penalty * u.far_fraction) *
+               wave_efficiency((u.pair ? ceil_div(u.tiles_m, 2) : u.tiles_m) * u.tiles_n * u.k_splits);
         // rows of a slab that are not contiguous in C cost a 32-byte sector per element
         if (u.a.row_elem_cstride != 1) c_bytes *= 8.0;
     }
     const double bytes = (double(p.sizeA) + double(p.sizeB)) * elt + c_bytes;
-    return c.launch_us + std::max(flops / (rate * 1e6), bytes / (c.hbm_gbs * 1e3));
+    return c.launch_us + std::max(flops / (rate * 1e6), bytes / (c.hbm_gbs * 1e3)) + extra_us;
+}
+
+// TF32 goes to the tcgen05 kernel whenever its tiles can be described to TMA.  FP64 takes the
+// cheapest of the TMA-fed tensor-path kernel, the gather tensor-path kernel (needs a tile per SM)
+// and the 64 x 64 CUDA-core tiles, by the cost table.
+int pick_kernel(const Problem& p, const UmmaSpec& u, const CostTable& c)
+{
+    if (u.eligible && u.elt == 4) return KERNEL_UMMA_TF32;
+    if (p.scalar_type != 1) return KERNEL_SIMT;
+    const char* k = std::getenv("TCONT_KERNEL");
+    if (k && std::strcmp(k, "simt") == 0) return KERNEL_SIMT;
+    int best = KERNEL_SIMT;
+    double best_us = contraction_us(p, KERNEL_SIMT, u, c);
+    const int64_t bn = p.Ntot <= 48 ? 32 : 64, bm = p.Ntot <= 48 ? 256 : 128;  // the gather kernel's smallest fitting tile
+    if (k && std::strcmp(k, "gather") == 0 && ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn) >= 148) return KERNEL_DMMA_F64;
+    if (ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn) >= 148) {
+        const double us = contraction_us(p, KERNEL_DMMA_F64, u, c);
+        if (us < best_us) best = KERNEL_DMMA_F64, best_us = us;
+    }
+    if (u.eligible && u.elt == 8) {
+        const double us = contraction_us(p, KERNEL_DMMA_F64_TMA, u, c);
+        if (us < best_us) best = KERNEL_DMMA_F64_TMA, best_us = us;
+    }
+    return best;
 }
 
 }  // namespace
@@ -533,6 +596,10 @@ CostTable load_cost_table()
         else if (key == "simt_f64_tflops") c.simt_f64_tflops = v;
         else if (key == "launch_us") c.launch_us = v;
         else if (key == "dmma_f64_tflops") c.dmma_f64_tflops = v;
+        else if (key == "dmma_f64_gather_tflops") c.dmma_f64_gather_tflops = v;
+        else if (key == "dmma_f64_gather8_tflops") c.dmma_f64_gather8_tflops = v;
+        else if (key == "dmma_f64_gather_narrow_tflops") c.dmma_f64_gather_narrow_tflops = v;
+        else if (key == "scatter_store_ps") c.scatter_store_ps = v;
         else if (key == "far_row_penalty") c.far_row_penalty = v;
     }
     return c;
@@ -592,7 +659,7 @@ int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* 
 
     UmmaSpec direct_umma;
     plan_umma(direct, &direct_umma);
-    const int direct_kernel = pick_kernel(direct, direct_umma);
+    const int direct_kernel = pick_kernel(direct, direct_umma, cost);
     pl.est_direct_us = contraction_us(direct, direct_kernel, direct_umma, cost);
 
     // Transpose-assisted candidate.  A role's transposed layout is
@@ -659,7 +726,7 @@ int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* 
     if (rc) return rc;
     UmmaSpec ttgt_umma;
     plan_umma(ttgt, &ttgt_umma);
-    const int ttgt_kernel = pick_kernel(ttgt, ttgt_umma);
+    const int ttgt_kernel = pick_kernel(ttgt, ttgt_umma, cost);
     TransposeSpec tA, tB;
     fill_transpose(roleA_src, roleA_dst, pl.ext_mode, pl.ext_val, &tA);
     fill_transpose(roleB_src, roleB_dst, pl.ext_mode, pl.ext_val, &tB);
@@ -755,7 +822,7 @@ std::string describe_plan(const Plan& pl)
     if (!u.eligible) o << ",\"why_not\":\"" << u.why_not << "\"";
     else {
         o << ",\"BM\":" << u.BM << ",\"BN\":" << u.BN << ",\"BK\":" << u.BK << ",\"stages\":" << u.stages
-          << ",\"pair\":" << (u.pair ? "true" : "false") << ",\"kc\":\"" << u.kc_names << "\",\"k_iters\":" << u.k_iters << ",\"tiles_m\":" << u.tiles_m << ",\"tiles_n\":" << u.tiles_n
+          << ",\"pair\":" << (u.pair ? "true" : "false") << ",\"kc\":\"" << u.kc_names << "\",\"k_iters\":" << u.k_iters << ",\"k_splits\":" << u.k_splits << ",\"tiles_m\":" << u.tiles_m << ",\"tiles_n\":" << u.tiles_n
           << ",\"a_major\":\"" << (u.a.major ? "MN" : "K") << "\",\"b_major\":\"" << (u.b.major ? "MN" : "K") << "\""
           << ",\"a_slab_w\":" << u.a.slab_w << ",\"b_slab_w\":" << u.b.slab_w << ",\"a_slabs_per_copy\":" << u.a.slabs_per_op << ",\"b_slabs_per_copy\":" << u.b.slabs_per_op << ",\"a_slabs\":" << u.a.slabs_per_tile
           << ",\"b_slabs\":" << u.b.slabs_per_tile << ",\"smem_bytes\":" << u.smem_bytes

@@ -83,6 +83,8 @@ struct UmmaSpec {
     int n_k_digits = 1;
     int64_t k_digit_ext[3] = {1, 1, 1};  // digit 0 = chunks of the chunked K mode
     int64_t k_iters = 1, tiles_m = 1, tiles_n = 1;
+    int k_splits = 1;               // ranges of the k iterations computed as separate work units (split-K)
+    int64_t k_iters_per_split = 1;
     double far_fraction = 0;  // share of a stage's bytes whose K rows are 64 KB or more apart in memory
     int raster_group = 16;
     bool pair = false;  // two-CTA clusters working on 256-row tiles (tcgen05 cta_group::2)
@@ -101,8 +103,12 @@ struct CostTable {
     double hbm_gbs = 6546.9;
     double umma_tf32_tflops = 600.0;
     double simt_f32_tflops = 20.0;
-    double simt_f64_tflops = 14.0;
-    double dmma_f64_tflops = 28.0;
+    double simt_f64_tflops = 11.0;
+    double dmma_f64_tflops = 30.0;          // TMA-fed tensor-path kernel
+    double dmma_f64_gather_tflops = 20.0;   // gather tensor-path kernel, 16-byte gathers
+    double dmma_f64_gather8_tflops = 12.0;  // gather tensor-path kernel, an operand on 8-byte gathers
+    double dmma_f64_gather_narrow_tflops = 4.5;  // gather tensor-path kernel, 256 x 32 tiles (N <= 48)
+    double scatter_store_ps = 28.0;         // per element of C stored on its own (TMA-fed FP64 kernel)
     double launch_us = 3.0;
     // Fraction of the tcgen05 rate lost per unit of staged bytes whose K rows lie 64 KB or more apart
     // (cfg5 on B200: 274 / 434 / 605 TFLOP/s with two thirds / one third / none of the bytes far-strided).

@@ -1,0 +1,66 @@
+// splitk_reduce.cu -- second pass of a split-K contraction: sums the partial tensors the contraction
+// kernel wrote (one per range of the contracted extent, each laid out like C) into C, in ascending
+// order of the split so that the result does not depend on scheduling.  Pure streaming: reads
+// splits * |C| elements, writes |C|.
+//
+// The reference has no counterpart: its generated kernels give one CTA the whole contracted extent
+// (backends/cogent/plan/generators/kernels/kernel_body.py) and its TTGT route leaves the split to
+// cuBLAS (backends/ttgt_cutt/src/ttgt_cutt.cpp:764-809).
+#include <algorithm>
+
+#include "kernels.hpp"
+
+namespace tcontb {
+namespace {
+
+template <typename T, typename V, int W>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const T* __restrict__ partial, T* __restrict__ C, long long elements,
+                                                           int splits, long long stride, bool vector_ok)
+{
+    const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (vector_ok) {
+        const long long nv = elements / W;
+        for (; i < nv; i += step) {
+            V acc = __ldcs(reinterpret_cast<const V*>(partial) + i);
+            for (int s = 1; s < splits; ++s) {
+                const V v = __ldcs(reinterpret_cast<const V*>(partial + static_cast<long long>(s) * stride) + i);
+                acc.x += v.x;
+                acc.y += v.y;
+                if constexpr (W == 4) {
+                    acc.z += v.z;
+                    acc.w += v.w;
+                }
+            }
+            __stcs(reinterpret_cast<V*>(C) + i, acc);
+        }
+        i = nv * W + (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x);
+    }
+    for (; i < elements; i += step) {
+        T acc = partial[i];
+        for (int s = 1; s < splits; ++s) acc += partial[static_cast<long long>(s) * stride + i];
+        C[i] = acc;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_splitk_reduce(const void* partial, void* C, long long elements, int splits, long long stride, int elt_bytes,
+                                 cudaStream_t stream)
+{
+    if (elements <= 0 || splits < 1) return cudaErrorInvalidValue;
+    const int w = elt_bytes == 8 ? 2 : 4;
+    const bool vector_ok = reinterpret_cast<uintptr_t>(partial) % 16 == 0 && reinterpret_cast<uintptr_t>(C) % 16 == 0 &&
+                           (stride * elt_bytes) % 16 == 0;
+    const long long work = vector_ok ? (elements + w - 1) / w : elements;
+    const unsigned grid = static_cast<unsigned>(std::min<long long>((work + 255) / 256, 148ll * 8));
+    if (elt_bytes == 8)
+        splitk_reduce_kernel<double, double2, 2><<<grid, 256, 0, stream>>>(static_cast<const double*>(partial), static_cast<double*>(C),
+                                                                            elements, splits, stride, vector_ok);
+    else
+        splitk_reduce_kernel<float, float4, 4><<<grid, 256, 0, stream>>>(static_cast<const float*>(partial), static_cast<float*>(C),
+                                                                          elements, splits, stride, vector_ok);
+    return cudaGetLastError();
+}
+
+}  // namespace tcontb

@@ -112,6 +112,24 @@ __device__ __forceinline__ void decode_tile(uint32_t tile, uint32_t tiles_m, uin
     *tn = local / rows;
 }
 
+// A unit of work: one tile, or with split-K one range of a tile's k iterations.  Units are numbered
+// tile * k_splits + split.
+struct WorkUnit {
+    uint32_t tm, tn, split;
+    int it0, n_it;
+};
+__device__ __forceinline__ WorkUnit decode_unit(uint32_t unit, const UmmaParams& p, uint32_t tiles_m, uint32_t tiles_n)
+{
+    WorkUnit w;
+    const uint32_t splits = static_cast<uint32_t>(p.k_splits);
+    const uint32_t tile = splits > 1 ? unit / splits : unit;
+    w.split = splits > 1 ? unit - tile * splits : 0u;
+    decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &w.tm, &w.tn);
+    w.it0 = static_cast<int>(w.split) * p.k_iters_per_split;
+    w.n_it = p.k_iters - w.it0 < p.k_iters_per_split ? p.k_iters - w.it0 : p.k_iters_per_split;
+    return w;
+}
+
 // Splits a slab index into its mixed-radix digits and returns the C offset of the slab start.
 // valid = false when the slab lies beyond the tensor.
 __device__ __forceinline__ long long slab_c_offset(const UmmaOperandDev& o, uint32_t slab, int* digit0, bool* valid)

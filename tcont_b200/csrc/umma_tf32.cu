@@ -194,7 +194,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     // Work units: 128-row tiles, or 256-row tile pairs; unit u of a pair covers row tiles 2u and 2u+1.
     const uint32_t tiles_m = PAIR ? (static_cast<uint32_t>(p.tiles_m) + 1u) / 2u : static_cast<uint32_t>(p.tiles_m);
     const uint32_t tiles_n = static_cast<uint32_t>(p.tiles_n);
-    const uint32_t total_tiles = tiles_m * tiles_n;
+    const uint32_t total_tiles = tiles_m * tiles_n * static_cast<uint32_t>(p.k_splits);  // work units (tile, k range)
     const uint32_t first_unit = PAIR ? blockIdx.x / 2u : blockIdx.x;
     const uint32_t unit_step = PAIR ? gridDim.x / 2u : gridDim.x;
 
@@ -219,8 +219,8 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         long long t_empty = 0;
 
         for (uint32_t tile = first_unit; tile < total_tiles; tile += unit_step) {
-            uint32_t tm, tn;
-            decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &tm, &tn);
+            const WorkUnit w = decode_unit(tile, p, tiles_m, tiles_n);
+            const uint32_t tm = w.tm, tn = w.tn;
             int base[kMaxTmaRank] = {0, 0, 0, 0, 0};
             if (active) {
                 const uint32_t s = is_a ? (PAIR ? 2u * tm + rank : tm) * SA + slab
@@ -246,8 +246,10 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                         if (o.row_digit_dim[0] == t) base[t] = o.oob_coord;
                 }
             }
-            int kd0 = 0, kd1 = 0, kd2 = 0;  // K digits: chunk of the chunked mode, then the other K modes
-            for (int it = 0; it < p.k_iters; ++it) {
+            // K digits: chunk of the chunked mode, then the other K modes
+            int kd0 = w.it0 % p.k_digit_ext[0], kd1 = (w.it0 / p.k_digit_ext[0]) % p.k_digit_ext[1];
+            int kd2 = w.it0 / (p.k_digit_ext[0] * p.k_digit_ext[1]);
+            for (int it = 0; it < w.n_it; ++it) {
                 const long long t0 = p.prof ? clock64() : 0;
                 const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + stage), phase ^ 1u, abort_flag));
                 if (p.prof) t_empty += clock64() - t0;
@@ -323,7 +325,8 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                 if (p.prof) t_tempty += clock64() - t0;
                 tcgen05_fence_after();
                 const uint32_t tmem_c = tmem_base + static_cast<uint32_t>(acc * p.BN);
-                for (int it = 0; it < p.k_iters; ++it) {
+                const int n_it = decode_unit(tile, p, tiles_m, tiles_n).n_it;
+                for (int it = 0; it < n_it; ++it) {
                     t0 = p.prof ? clock64() : 0;
                     ok = ok && mbar_wait(smem_u32(bar_full + stage), phase, abort_flag);
                     if (p.prof) t_full += clock64() - t0;
@@ -371,8 +374,8 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         long long iter = 0;
         long long t_tfull = 0, t_epi = clock64();
         for (uint32_t tile = first_unit; tile < total_tiles; tile += unit_step, ++iter) {
-            uint32_t tm, tn;
-            decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &tm, &tn);
+            const WorkUnit w = decode_unit(tile, p, tiles_m, tiles_n);
+            const uint32_t tm = w.tm, tn = w.tn;
             const int acc = static_cast<int>(iter & 1);
             const uint32_t acc_parity = static_cast<uint32_t>((iter >> 1) & 1);
             // this thread's row of C
@@ -423,7 +426,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             tcgen05_fence_after();
             if (ok) {
-                float* crow = p.C + row_off;
+                float* crow = p.C + static_cast<long long>(w.split) * p.split_stride + row_off;
                 const long long col_stride = p.b.row_elem_cstride;
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * p.BN);
                 const int nchunks = p.BN >> 5;
@@ -512,7 +515,7 @@ cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void*
     const CUtensorMap& ta = *static_cast<const CUtensorMap*>(tmapA);
     const CUtensorMap& tb = *static_cast<const CUtensorMap*>(tmapB);
     if (p.pair) {
-        const long long units = ((p.tiles_m + 1) / 2) * p.tiles_n;
+        const long long units = ((p.tiles_m + 1) / 2) * p.tiles_n * p.k_splits;
         if (units <= 0) return cudaErrorInvalidValue;
         const long long clusters = units < num_sms / 2 ? units : num_sms / 2;
         cudaLaunchConfig_t cfg = {};
@@ -529,7 +532,7 @@ cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void*
         cfg.numAttrs = 1;
         return cudaLaunchKernelEx(&cfg, umma_tf32_kernel<true>, ta, tb, p);
     }
-    const long long total = p.tiles_m * p.tiles_n;
+    const long long total = p.tiles_m * p.tiles_n * p.k_splits;
     if (total <= 0) return cudaErrorInvalidValue;
     const unsigned grid = static_cast<unsigned>(total < num_sms ? total : num_sms);
     umma_tf32_kernel<false><<<grid, kThreads, smem_bytes, stream>>>(ta, tb, p);

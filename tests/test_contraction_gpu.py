@@ -77,15 +77,25 @@ UMMA_SHAPES = {
     "three_k": Contraction("ab", "axyz", "xyzb", dict(a=64, b=48, x=8, y=3, z=5), F32),
     "swapped": Contraction("abc", "db", "adc", dict(a=64, c=6, b=40, d=48), F32),               # C's stride-1 mode in the right operand
     "case31_like": Contraction("abcdef", "dega", "gfbc", dict(a=8, b=4, c=4, d=24, e=4, f=8, g=24), F32),
+    "long_k": Contraction("ab", "acd", "dbc", dict(a=312, b=296, c=40, d=36), F32),             # 30 tiles, 45 k iterations: split-K
+    "long_k_ragged": Contraction("ab", "ak", "kb", dict(a=200, b=120, k=1000), F32),            # last k range shorter than the others
 }
 
 
 @pytest.mark.parametrize("name", list(UMMA_SHAPES))
-def test_tensor_core_shapes(engine, oracle, name):
+@pytest.mark.parametrize("splitk", ["auto", "1", "3"])
+def test_tensor_core_shapes(engine, oracle, monkeypatch, name, splitk):
+    """tcgen05 kernel; k ranges as the planner cuts them, not at all, and forced to three."""
+    if splitk != "auto":
+        monkeypatch.setenv("TCONT_SPLITK", splitk)
     c = UMMA_SHAPES[name]
     A, B = oracle.inputs(c, 77, -1.0, 1.0)
     out, desc = run_contraction(engine, c, A, B, 0)
     assert desc["kernel"] == "umma_tf32", desc["umma"]
+    if splitk == "1":
+        assert desc["umma"]["k_splits"] == 1
+    if splitk == "auto" and name.startswith("long_k"):
+        assert desc["umma"]["k_splits"] > 1
     check(oracle, c, A, B, out, desc)
 
 
@@ -96,7 +106,10 @@ FP64_SHAPES = {
     "gemm_mn_k": Contraction("ab", "ak", "kb", dict(a=1200, b=1000, k=200), F64),                      # MN-major A (merged boxes), K-major B
     "two_k_long": Contraction("abcd", "aebf", "cfde", dict(a=64, b=40, c=48, d=18, e=24, f=10), F64),  # both MN-major, two K modes
     "kmajor_long": Contraction("ab", "ka", "kb", dict(a=1537, b=1409, k=262), F64),                   # K-major boxes, ragged everywhere
+    "scattered_store": Contraction("abc", "bda", "dc", dict(a=160, b=160, c=24, d=200), F64),          # slab mode b is not C's stride-1 mode
     "case21_like": Contraction("abcd", "aebf", "fdec", dict(a=72, b=24, c=24, d=72, e=24, f=16), F64),
+    "long_k": Contraction("ab", "acd", "dbc", dict(a=312, b=296, c=40, d=36), F64),                  # 15 tiles, 108 k iterations: split-K
+    "long_k_ragged": Contraction("ab", "ak", "kb", dict(a=200, b=120, k=1000), F64),
 }
 
 
@@ -109,12 +122,27 @@ def test_fp64_tensor_path(engine, oracle, monkeypatch, name, kernel):
     c = FP64_SHAPES[name]
     A, B = oracle.inputs(c, 31, -1.0, 1.0)
     out, desc = run_contraction(engine, c, A, B, 1)
-    assert desc["kernel"] in (("dmma_f64",) if kernel == "gather" else ("dmma_f64", "dmma_f64_tma"))
+    # (TCONT_KERNEL=gather forces the gather kernel wherever it has a tile per SM)
+    assert desc["kernel"] in (("dmma_f64", "simt") if kernel == "gather" else ("dmma_f64", "dmma_f64_tma", "simt"))
+    if kernel == "gather" and name in ("ragged4d", "cfg3_like", "kmajor", "gemm_mn_k", "two_k_long", "case21_like"):
+        assert desc["kernel"] == "dmma_f64"
+    if kernel == "auto" and name.startswith("long_k"):
+        assert desc["kernel"] == "dmma_f64_tma" and desc["umma"]["k_splits"] > 1
     check(oracle, c, A, B, out, desc)
 
 
-def test_fp64_tma_kernel_is_used_for_long_k(engine):
-    for name in ("gemm_mn_k", "two_k_long", "kmajor_long", "case21_like"):
+@pytest.mark.parametrize("name", ["gemm_mn_k", "kmajor_long", "two_k_long"])
+def test_fp64_split_k_forced(engine, oracle, monkeypatch, name):
+    monkeypatch.setenv("TCONT_SPLITK", "3")
+    c = FP64_SHAPES[name]
+    A, B = oracle.inputs(c, 32, -1.0, 1.0)
+    out, desc = run_contraction(engine, c, A, B, 1)
+    assert desc["kernel"] == "dmma_f64_tma" and desc["umma"]["k_splits"] == 3
+    check(oracle, c, A, B, out, desc)
+
+
+def test_fp64_tma_kernel_is_picked(engine):
+    for name in ("cfg3_like", "kmajor", "gemm_mn_k", "two_k_long", "kmajor_long", "scattered_store", "case21_like", "long_k"):
         d = engine.plan(to_equation(engine, FP64_SHAPES[name], 1)).describe()
         assert d["kernel"] == "dmma_f64_tma", (name, d["kernel"], d["umma"])
 

@@ -2,6 +2,7 @@
 import pytest
 
 from cases import CONFIGS, fixture_contraction, golden_fixtures, to_equation
+from oracle_lib import Contraction
 
 
 def describe(engine, c, selection=0):
@@ -55,8 +56,33 @@ def test_configs_pick_the_intended_kernels(engine):
     assert d5["backend"] == "ttgt" and d5["transpose_a"] == [0, 3, 1, 2] and d5["transpose_b"] is None
     assert d5["kernel"] == "umma_tf32" and d5["umma"]["k_iters"] == 512 and d5["umma"]["kc"] == "f"
     assert d2["umma"]["pair"] is False and d2["umma"]["a_slabs_per_copy"] == 4
-    assert describe(engine, CONFIGS["cfg3"][0])["kernel"] == "dmma_f64"   # a 128x128 tile per SM and more
-    assert describe(engine, CONFIGS["cfg1"][0])["kernel"] == "simt"
+    d3 = describe(engine, CONFIGS["cfg3"][0])   # TMA-fed FP64 kernel: one 128-byte row of 16 doubles per box row
+    assert d3["backend"] == "direct" and d3["kernel"] == "dmma_f64_tma"
+    assert (d3["umma"]["BN"], d3["umma"]["BK"], d3["umma"]["stages"], d3["umma"]["k_iters"]) == (64, 16, 8, 3)
+    assert d3["umma"]["coalesced_store"] and d3["umma"]["smem_bytes"] <= 227 * 1024
+
+
+def test_fp64_kernel_choice_follows_the_cost_table(engine, monkeypatch):
+    F64 = 1
+    # a slab mode that is not C's stride-1 mode: stores would be scattered, one transpose of A is cheaper
+    c31 = Contraction("abcdef", "dega", "gfbc", dict(a=24, b=16, c=16, d=24, e=16, f=16, g=24), F64)
+    d = describe(engine, c31)
+    assert d["backend"] == "ttgt" and d["kernel"] == "dmma_f64_tma" and d["umma"]["coalesced_store"]
+    # ... unless the contracted extent is long enough to pay for them (and A is too large to move)
+    c1 = Contraction("abc", "bda", "dc", dict(a=312, b=312, c=24, d=312), F64)
+    d = describe(engine, c1)
+    assert d["backend"] == "direct" and d["kernel"] == "dmma_f64_tma" and not d["umma"]["coalesced_store"]
+    # operands that are K-major on different contracted modes cannot be described to TMA where they lie
+    c28 = Contraction("abcd", "eafb", "fdec", dict(a=72, b=72, c=72, d=72, e=72, f=72), F64)
+    d = describe(engine, c28)
+    assert d["backend"] == "ttgt" and d["kernel"] == "dmma_f64_tma"
+    monkeypatch.setenv("TCONT_KERNEL", "gather")
+    assert describe(engine, c28, 1)["kernel"] == "dmma_f64"
+    monkeypatch.setenv("TCONT_KERNEL", "simt")
+    assert describe(engine, c28, 1)["kernel"] == "simt"
+    monkeypatch.delenv("TCONT_KERNEL")
+    # tiny problems stay on the CUDA-core tiles
+    assert describe(engine, CONFIGS["cfg1"][0])["kernel"] in ("simt", "dmma_f64_tma")
 
 
 def test_every_reference_pattern_plans(engine):

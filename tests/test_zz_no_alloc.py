@@ -52,11 +52,9 @@ def _both(engine, oracle, c):
 def test_no_alloc_matches_regular_entry_point(engine, oracle, c):
     regular, outs, (A, B) = _both(engine, oracle, c)
     for got in outs:
-        if c.scalar_type == F64:
-            np.testing.assert_array_equal(got, regular)
-        else:
-            diff, nonfinite = oracle.compare(regular, got, F32)
-            assert (diff, nonfinite) == (0, 0)
+        # the regular entry point may run another kernel (tensor path, split-K): same tolerance as against the oracle
+        diff, nonfinite = oracle.compare(regular, got, c.scalar_type)
+        assert (diff, nonfinite) == (0, 0)
         diff, nonfinite = oracle.compare(oracle.contract(c, A, B), got, c.scalar_type)
         assert (diff, nonfinite) == (0, 0)
 
