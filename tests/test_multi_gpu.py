@@ -1,7 +1,9 @@
 """GPU (needs 2 or more devices): several GPUs behind ONE run object, the form the reference's
 unchanged single-process harness drives (TCONT_NUM_GPUS / TCONT_SPLIT in the environment).  The
-contraction is cut along an external mode, so every output element is computed by exactly one GPU
-with the same kernel as on a single device: results must be bit-identical."""
+contraction is cut along an external mode, so every output element is computed by exactly one GPU.
+A shard is planned as a contraction of its own, so it may run another kernel or other k ranges
+than the full problem does: results must agree within the reference's tolerance, and be
+bit-identical when split-K is off and both plans run the same kernel."""
 import numpy as np
 import pytest
 
@@ -50,7 +52,9 @@ def test_two_gpus_equal_one(engine, oracle, monkeypatch, c, split):
     assert multi.device_status() == 0 and ms > 0 and launches >= 6
     np.testing.assert_array_equal(engine.input_left_host_data(multi), A)    # the global inputs, as the harness's verifier needs
     np.testing.assert_array_equal(engine.input_right_host_data(multi), B)
-    np.testing.assert_array_equal(got, want)
+    assert oracle.compare(want, got, c.scalar_type) == (0, 0)
+    if c.scalar_type == F64:
+        assert oracle.compare(oracle.contract(c, A, B), got, F64) == (0, 0)
 
 
 @needs_two
