@@ -14,8 +14,8 @@
 //               and 64 columns (mixed-radix slab arithmetic, the same as the tcgen05 epilogue),
 //               double-buffered per group behind mbarriers
 //   warps 4-7   consumer group 0, warps 8-11 consumer group 1.  A group is 2 x 2 warps with a
-//               64 x 32 warp tile (8 x 4 accumulator fragments) and takes every other tile of the
-//               block.  Group 1 starts half a main loop late, so one group's stores fall into the
+//               64 x 32 warp tile (8 x 4 accumulator fragments; 64 x 16 in the 128 x 32 variant for
+//               narrow N) and takes every other tile of the block.  Group 1 starts half a main loop late, so one group's stores fall into the
 //               other's main loop instead of both storing with the FP64 pipe idle.
 // Fragment rows are permuted so that one 16-byte shared load of an MN-major operand feeds two
 // fragments (rows 2 r and 2 r + 1 of a 16-row slab) without bank conflicts, and the MMA is issued
@@ -36,8 +36,8 @@ namespace tcontb {
 namespace {
 
 constexpr int kThreads64 = 384;
-constexpr int kBM = 128, kBN = 64;
-constexpr uint32_t kTabBytes = (kBM + kBN) * 8u;  // one tile's row and column offsets
+constexpr int kBM = 128, kMaxBN = 64;
+constexpr uint32_t kTabBytes = (kBM + kMaxBN) * 8u;  // one tile's row and column offsets
 
 __device__ __forceinline__ double ld_shared_f64(uint32_t addr)
 {
@@ -101,17 +101,17 @@ __device__ __forceinline__ void load_all(double (&f)[N], const FragAddr& q, uint
     }
 }
 
-// One k4 step of a warp: 32 MMAs on the current fragments; with PF the fragment loads of the next
+// One k4 step of a warp: 8 NF MMAs on the current fragments (NF = 4 or 2 column fragments); with PF the fragment loads of the next
 // step are issued between them, where the FP64 tensor pipe leaves issue slots free.
 // acc[i][j][h]: row m = 16 (i / 2) + 4 (lane % 4) + 2 h + (i % 2), column n = 16 (j / 2) + 2 (lane / 4) + (j % 2).
-template <bool PF, bool AMN, bool BMN>
-__device__ __forceinline__ void mma_step(double (&acc)[8][4][2], const double (&ac)[8], const double (&bc)[4], double (&an)[8],
-                                         double (&bn)[4], const FragAddr& qa, const FragAddr& qb, uint32_t a_pitch, uint32_t b_pitch)
+template <bool PF, bool AMN, bool BMN, int NF>
+__device__ __forceinline__ void mma_step(double (&acc)[8][NF][2], const double (&ac)[8], const double (&bc)[NF], double (&an)[8],
+                                         double (&bn)[NF], const FragAddr& qa, const FragAddr& qb, uint32_t a_pitch, uint32_t b_pitch)
 {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) dmma_m8n8k4(acc[i][j], bc[j], ac[i]);
+        for (int j = 0; j < NF; ++j) dmma_m8n8k4(acc[i][j], bc[j], ac[i]);
         if (PF) {
             if (AMN) {
                 if ((i & 1) == 0) ld_shared_v2f64(qa.q0 + static_cast<uint32_t>(i >> 1) * a_pitch, an[i], an[i + 1]);
@@ -119,15 +119,15 @@ __device__ __forceinline__ void mma_step(double (&acc)[8][4][2], const double (&
                 an[i] = ld_shared_f64(((i & 1) ? qa.q1 : qa.q0) + static_cast<uint32_t>(i >> 1) * 2048u);
             }
             if (BMN) {
-                if (i == 1 || i == 3) ld_shared_v2f64(qb.q0 + static_cast<uint32_t>(i >> 1) * b_pitch, bn[i - 1], bn[i]);
+                if ((i == 1 || i == 3) && i < NF) ld_shared_v2f64(qb.q0 + static_cast<uint32_t>(i >> 1) * b_pitch, bn[i - 1], bn[i]);
             } else {
-                if (i < 4) bn[i] = ld_shared_f64(((i & 1) ? qb.q1 : qb.q0) + static_cast<uint32_t>(i >> 1) * 2048u);
+                if (i < NF) bn[i] = ld_shared_f64(((i & 1) ? qb.q1 : qb.q0) + static_cast<uint32_t>(i >> 1) * 2048u);
             }
         }
     }
 }
 
-template <bool AMN, bool BMN>
+template <bool AMN, bool BMN, int NF>
 __global__ void __launch_bounds__(kThreads64, 1)
 dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                 const __grid_constant__ UmmaParams p)
@@ -272,6 +272,7 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 for (int e3 = 0; e3 < 3; ++e3) {
                     const int e = bt + e3 * 64;
                     const bool is_row = e < kBM;
+                    if (!is_row && e - kBM >= NF * 16) continue;
                     const UmmaOperandDev& o = is_row ? p.a : p.b;
                     const int idx = is_row ? e : e - kBM;
                     const int sl = idx / o.slab_w, in = idx % o.slab_w;
@@ -292,13 +293,14 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         const uint32_t first = static_cast<uint32_t>(grp) * ring;
         const uint32_t a_pitch = static_cast<uint32_t>(p.a.slab_bytes), b_pitch = static_cast<uint32_t>(p.b.slab_bytes);
         const uint32_t a_thread = AMN ? static_cast<uint32_t>(wm * 4) * a_pitch : (static_cast<uint32_t>(wm * 64) + 2u * fr) * 128u;
-        const uint32_t b_thread = a_tile_bytes + (BMN ? static_cast<uint32_t>(wn * 2) * b_pitch : (static_cast<uint32_t>(wn * 32) + 2u * fr) * 128u);
+        const uint32_t b_thread = a_tile_bytes + (BMN ? static_cast<uint32_t>(wn * (NF / 2)) * b_pitch
+                                                      : (static_cast<uint32_t>(wn * NF * 8) + 2u * fr) * 128u);
 
-        double acc[8][4][2];
+        double acc[8][NF][2];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+            for (int j = 0; j < NF; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
 
         uint32_t stage = 0, phase = 0;
         const bool prof = p.prof != nullptr && (threadIdx.x & 127) == 0 && grp == 0;
@@ -321,19 +323,19 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 tile_ok = tile_ok && ok;
                 if (ok) {
                     const uint32_t sb = smem_u32(smem) + ps * stage_bytes;
-                    double fa0[8], fb0[4], fa1[8], fb1[4];
+                    double fa0[8], fb0[NF], fa1[8], fb1[NF];
                     FragAddr qa = frag_addr<AMN>(sb + a_thread, fk, fr), qb = frag_addr<BMN>(sb + b_thread, fk, fr);
                     load_all<AMN, 8>(fa0, qa, a_pitch);
-                    load_all<BMN, 4>(fb0, qb, b_pitch);
+                    load_all<BMN, NF>(fb0, qb, b_pitch);
                     qa = frag_addr<AMN>(sb + a_thread, 4u + fk, fr), qb = frag_addr<BMN>(sb + b_thread, 4u + fk, fr);
-                    mma_step<true, AMN, BMN>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
+                    mma_step<true, AMN, BMN, NF>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
                     if (p.BK == 16) {
                         qa = frag_addr<AMN>(sb + a_thread, 8u + fk, fr), qb = frag_addr<BMN>(sb + b_thread, 8u + fk, fr);
-                        mma_step<true, AMN, BMN>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
+                        mma_step<true, AMN, BMN, NF>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
                         qa = frag_addr<AMN>(sb + a_thread, 12u + fk, fr), qb = frag_addr<BMN>(sb + b_thread, 12u + fk, fr);
-                        mma_step<true, AMN, BMN>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
+                        mma_step<true, AMN, BMN, NF>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
                     }
-                    mma_step<false, AMN, BMN>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
+                    mma_step<false, AMN, BMN, NF>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(bar_empty + ps));  // this warp is done reading the stage
@@ -351,10 +353,10 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             if (prof) { const long long t1 = clock64(); t_tab += t1 - t0; t0 = t1; }
 
             // store: four consecutive rows per (fragment pair, column fragment), 32 bytes when aligned
-            long long cn[4];
+            long long cn[NF];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                cn[j] = ld_shared_s64(col_tab + (static_cast<uint32_t>(wn * 32 + 16 * (j >> 1) + (j & 1)) + 2u * fr) * 8u);
+            for (int j = 0; j < NF; ++j)
+                cn[j] = ld_shared_s64(col_tab + (static_cast<uint32_t>(wn * NF * 8 + 16 * (j >> 1) + (j & 1)) + 2u * fr) * 8u);
 #pragma unroll
             for (int pr = 0; pr < 4; ++pr) {
                 const uint32_t r = static_cast<uint32_t>(wm * 64 + 16 * pr) + 4u * fk;
@@ -362,7 +364,7 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 const long long cm2 = ld_shared_s64(row_tab + r * 8u + 16u), cm3 = ld_shared_s64(row_tab + r * 8u + 24u);
                 const bool run4 = cm0 >= 0 && cm1 == cm0 + 1 && cm2 == cm0 + 2 && cm3 == cm0 + 3;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < NF; ++j) {
                     if (tile_ok && cn[j] >= 0) {
                         double* dst = C + cm0 + cn[j];
                         if (run4 && (reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
@@ -395,34 +397,47 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
     if (threadIdx.x == 0 && ld_shared_u32(abort_flag)) atomicMax(p.status, 1);
 }
 
-template <bool AMN, bool BMN>
+template <bool AMN, bool BMN, int NF>
 cudaError_t launch_variant(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, unsigned grid, cudaStream_t stream)
 {
-    dmma_tma_kernel<AMN, BMN><<<grid, kThreads64, smem_bytes, stream>>>(*static_cast<const CUtensorMap*>(tmapA),
-                                                                         *static_cast<const CUtensorMap*>(tmapB), p);
+    dmma_tma_kernel<AMN, BMN, NF><<<grid, kThreads64, smem_bytes, stream>>>(*static_cast<const CUtensorMap*>(tmapA),
+                                                                             *static_cast<const CUtensorMap*>(tmapB), p);
     return cudaGetLastError();
+}
+
+template <int NF>
+cudaError_t launch_width(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, unsigned grid, cudaStream_t stream)
+{
+    if (p.a.major && p.b.major) return launch_variant<true, true, NF>(p, tmapA, tmapB, smem_bytes, grid, stream);
+    if (p.a.major) return launch_variant<true, false, NF>(p, tmapA, tmapB, smem_bytes, grid, stream);
+    if (p.b.major) return launch_variant<false, true, NF>(p, tmapA, tmapB, smem_bytes, grid, stream);
+    return launch_variant<false, false, NF>(p, tmapA, tmapB, smem_bytes, grid, stream);
+}
+
+template <int NF>
+cudaError_t configure_width(int smem_bytes)
+{
+    cudaError_t e = cudaFuncSetAttribute(dmma_tma_kernel<false, false, NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<false, true, NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<true, false, NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<true, true, NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    return e;
 }
 
 }  // namespace
 
 cudaError_t dmma_tma_configure(int smem_bytes)
 {
-    cudaError_t e = cudaFuncSetAttribute(dmma_tma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    return e;
+    const cudaError_t e = configure_width<4>(smem_bytes);
+    return e == cudaSuccess ? configure_width<2>(smem_bytes) : e;
 }
 
 cudaError_t launch_dmma_tma(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms, cudaStream_t stream)
 {
     const long long total = p.tiles_m * p.tiles_n * p.k_splits;
-    if (total <= 0 || p.k_splits < 1 || p.stages < 2 || (p.stages & 1)) return cudaErrorInvalidValue;
+    if (total <= 0 || p.k_splits < 1 || p.stages < 2 || (p.stages & 1) || (p.BN != 64 && p.BN != 32)) return cudaErrorInvalidValue;
     const unsigned grid = static_cast<unsigned>(total < num_sms ? total : num_sms);
-    if (p.a.major && p.b.major) return launch_variant<true, true>(p, tmapA, tmapB, smem_bytes, grid, stream);
-    if (p.a.major) return launch_variant<true, false>(p, tmapA, tmapB, smem_bytes, grid, stream);
-    if (p.b.major) return launch_variant<false, true>(p, tmapA, tmapB, smem_bytes, grid, stream);
-    return launch_variant<false, false>(p, tmapA, tmapB, smem_bytes, grid, stream);
+    return p.BN == 64 ? launch_width<4>(p, tmapA, tmapB, smem_bytes, grid, stream) : launch_width<2>(p, tmapA, tmapB, smem_bytes, grid, stream);
 }
 
 }  // namespace tcontb

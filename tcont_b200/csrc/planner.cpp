@@ -219,12 +219,14 @@ void finish_operand(const Problem& p, const std::vector<int>& t, const std::vect
     const int W = p.scalar_type == 1 ? 16 : 32;
     if (o->major == 0) {
         // K-major: rows per slab = the largest power of two (8..tile height) that pads the slab
-        // mode by at most 15 %; failing that, the one that pads least.
+        // mode by at most 15 % (TF32, where fewer and larger TMA boxes matter more) or 3 % (FP64,
+        // where padded rows cost FP64 tensor time); failing that, the one that pads least.
+        const double limit = p.scalar_type == 1 ? 1.03 : 1.15;
         int best = 8;
         double best_waste = 1e30;
         for (int w = 8; w <= tile_rows && w <= max_slab_rows; w *= 2) {
             const double waste = double(ceil_div(o->slab_mode_ext, w) * w) / double(o->slab_mode_ext);
-            const bool ok = waste <= 1.15, best_ok = best_waste <= 1.15;
+            const bool ok = waste <= limit, best_ok = best_waste <= limit;
             if ((ok && (!best_ok || w > best)) || (!ok && !best_ok && waste < best_waste - 1e-12)) {
                 best = w;
                 best_waste = waste;
@@ -386,7 +388,11 @@ void plan_umma(const Problem& p, UmmaSpec* u)
     // still yields at least one tile per SM; otherwise the narrowest admissible one.
     int bn = 32;
     if (f64) {
-        bn = 64;  // the FP64 kernel has one tile shape: 128 x 64
+        // the FP64 kernel has 128 x 64 and 128 x 32 tiles: the narrow one where it pads N less
+        UmmaOperand probe = u->b;
+        finish_operand(p, p.B, p.N, 32, BK, kdigits, &probe);
+        const int64_t padded = probe.total_slabs * probe.slab_w;
+        bn = ceil_div(padded, 32) * 32 < ceil_div(padded, 64) * 64 ? 32 : 64;
     } else {
         UmmaOperand probe = u->b;
         finish_operand(p, p.B, p.N, 32, BK, kdigits, &probe);
