@@ -62,7 +62,13 @@ __device__ __forceinline__ void st_global_cs_v4f64(double* p, double a, double b
     asm volatile("st.global.cs.v4.f64 [%0], {%1, %2, %3, %4};" ::"l"(p), "d"(a), "d"(b), "d"(c), "d"(d) : "memory");
 }
 
-// Where a thread finds its fragments of one operand for one k (k = k4 + lane % 4):
+// Which k a lane feeds into step t of a stage: k = 8 (t / 2) + 2 fk + ((fk ^ t) & 1), fk = lane % 4.
+// Any assignment works as long as both operands use the same one; with this one the four rows an
+// MN-major 16-byte load touches per quarter warp differ in k / 2, which after the XOR swizzle puts
+// the quarter's eight 16-byte chunks into eight different bank groups.
+__device__ __forceinline__ uint32_t step_k(uint32_t t, uint32_t fk) { return 8u * (t >> 1) + 2u * fk + ((fk ^ t) & 1u); }
+
+// Where a thread finds its fragments of one operand for one k:
 //   MN-major (rows of the stage are k, 16 consecutive m per row, slabs of 16 m `pitch` apart):
 //     one 16-byte load at  q0 + pair * pitch  holds fragments 2 pair and 2 pair + 1
 //   K-major (rows of the stage are m, 16 consecutive k per row):
@@ -324,15 +330,15 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 if (ok) {
                     const uint32_t sb = smem_u32(smem) + ps * stage_bytes;
                     double fa0[8], fb0[NF], fa1[8], fb1[NF];
-                    FragAddr qa = frag_addr<AMN>(sb + a_thread, fk, fr), qb = frag_addr<BMN>(sb + b_thread, fk, fr);
+                    FragAddr qa = frag_addr<AMN>(sb + a_thread, step_k(0, fk), fr), qb = frag_addr<BMN>(sb + b_thread, step_k(0, fk), fr);
                     load_all<AMN, 8>(fa0, qa, a_pitch);
                     load_all<BMN, NF>(fb0, qb, b_pitch);
-                    qa = frag_addr<AMN>(sb + a_thread, 4u + fk, fr), qb = frag_addr<BMN>(sb + b_thread, 4u + fk, fr);
+                    qa = frag_addr<AMN>(sb + a_thread, step_k(1, fk), fr), qb = frag_addr<BMN>(sb + b_thread, step_k(1, fk), fr);
                     mma_step<true, AMN, BMN, NF>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
                     if (p.BK == 16) {
-                        qa = frag_addr<AMN>(sb + a_thread, 8u + fk, fr), qb = frag_addr<BMN>(sb + b_thread, 8u + fk, fr);
+                        qa = frag_addr<AMN>(sb + a_thread, step_k(2, fk), fr), qb = frag_addr<BMN>(sb + b_thread, step_k(2, fk), fr);
                         mma_step<true, AMN, BMN, NF>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
-                        qa = frag_addr<AMN>(sb + a_thread, 12u + fk, fr), qb = frag_addr<BMN>(sb + b_thread, 12u + fk, fr);
+                        qa = frag_addr<AMN>(sb + a_thread, step_k(3, fk), fr), qb = frag_addr<BMN>(sb + b_thread, step_k(3, fk), fr);
                         mma_step<true, AMN, BMN, NF>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
                     }
                     mma_step<false, AMN, BMN, NF>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
