@@ -38,7 +38,7 @@ WORKLOADS = {
 }
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
 # captures summarised under profiles/; None where no capture of that workload exists.
-NCU_TRAFFIC = {"cfg2": 501.7e6, "cfg4": 964.4e6}
+NCU_TRAFFIC = {"cfg2": 501.7e6, "cfg4": 964.4e6, "cfg3": 6 * (1980.4e6 + 53.7e6)}  # cfg3: k=4 capture scaled by the tile count
 REF_CASE = {"cfg1": 21, "cfg2": 18}   # reference loop nests with the same mode pattern (tccg_verify.cpp:660-689, :567-592)
 
 

@@ -66,11 +66,29 @@ def calibrate() -> dict:
     table["umma_tf32_tflops"], k = _rate(tc, api, torch, *gemm, F32)
     assert k == "umma_tf32", k
     table["simt_f32_tflops"], _ = _rate(tc, api, torch, ("ab", "ka", "kb"), dict(a=4096, b=4096, k=1024), F32, env={"TCONT_KERNEL": "simt"})
-    table["dmma_f64_tflops"], k = _rate(tc, api, torch, ("ab", "ak", "bk"), dict(a=4096, b=4096, k=2048), F64)
+    gemm64 = (("ab", "ak", "kb"), dict(a=4096, b=4096, k=2048))
+    table["dmma_f64_tflops"], k = _rate(tc, api, torch, *gemm64, F64)
+    assert k == "dmma_f64_tma", k
+    table["dmma_f64_gather_tflops"], k = _rate(tc, api, torch, *gemm64, F64, env={"TCONT_KERNEL": "gather"})
+    assert k == "dmma_f64", k
+    # one operand whose stride-1 mode leads neither its rows nor the contracted modes: 8-byte gathers
+    table["dmma_f64_gather8_tflops"], k = _rate(tc, api, torch, ("abc", "akc", "kb"), dict(a=2, b=2048, c=2048, k=2048), F64,
+                                                env={"TCONT_KERNEL": "gather"})
+    assert k == "dmma_f64", k
+    table["dmma_f64_gather_narrow_tflops"], k = _rate(tc, api, torch, ("abc", "dca", "bd"), dict(a=312, b=24, c=296, d=312), F64,
+                                                      env={"TCONT_KERNEL": "gather"})
     assert k == "dmma_f64", k
     table["simt_f64_tflops"], _ = _rate(tc, api, torch, ("ab", "ak", "bk"), dict(a=4096, b=4096, k=1024), F64, env={"TCONT_KERNEL": "simt"})
+    # scattered stores of the TMA-fed FP64 kernel: two contractions of the same size, one whose tile rows
+    # run along C's stride-1 mode and one whose rows do not; the difference per element of C
+    ext = dict(a=312, b=312, c=24, d=312)
+    t_rows, k1 = _rate(tc, api, torch, ("abc", "dca", "bd"), dict(a=312, b=24, c=312, d=312), F64)
+    t_scat, k2 = _rate(tc, api, torch, ("abc", "bda", "dc"), ext, F64)
+    if k1 == k2 == "dmma_f64_tma":
+        flops = 2.0 * 312 * 312 * 24 * 312
+        table["scatter_store_ps"] = max(0.0, (flops / (t_scat * 1e12) - flops / (t_rows * 1e12)) / (312 * 312 * 24) * 1e12)
     # far-row penalty: the same 4-D contraction with the chunked contracted mode near (f) and far (e) in B
-    shape = (("abcd", "aebf", "cfde"), dict(a=128, b=64, c=128, d=64, e=64, f=64))
+    shape = (("abcd", "aebf", "cfde"), dict(a=128, b=128, c=128, d=128, e=64, f=64))
     near, _ = _rate(tc, api, torch, *shape, F32, iters=3, env={"TCONT_UMMA_KC": "f"})
     far, _ = _rate(tc, api, torch, *shape, F32, iters=3, env={"TCONT_UMMA_KC": "e"})
     # kc=f: A's rows are far (1/3 of a stage's bytes); kc=e: B's rows are far (2/3): rate ~ 1 - p * share

@@ -365,7 +365,12 @@ void plan_umma(const Problem& p, UmmaSpec* u)
     const int64_t kc_ext = p.modes[static_cast<size_t>(kc)].extent;
     u->kc_names = p.modes[static_cast<size_t>(kc)].names;
     int BK = W;  // a K-major operand brings 128 bytes of K per row
-    if (!a_kmajor && !b_kmajor) BK = f64 ? (kc_ext <= 8 ? 8 : 16) : (kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32);
+    // Both operands MN-major: the k chunk may be narrower than a 128-byte row.  FP64 takes 8 instead of
+    // 16 where that spares more than 15 % of zero-filled k (24 = 3 x 8 against 2 x 16).
+    if (!a_kmajor && !b_kmajor) {
+        if (f64) BK = kc_ext <= 8 || double(ceil_div(kc_ext, 16) * 16) > 1.15 * double(ceil_div(kc_ext, 8) * 8) ? 8 : 16;
+        else BK = kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32;
+    }
     u->BK = BK;
     std::vector<int> kdigits{kc};
     for (int id : p.K)
@@ -531,12 +536,17 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
     };
     if (kernel == KERNEL_SIMT && p.scalar_type == 1)
         rate *= wave_efficiency(ceil_div(p.Mtot, 64) * ceil_div(p.Ntot, 64)) / padded(64, 64);
+    // TMA-fed kernels: slabs and k chunks are whole, ragged extents are zero-filled and multiplied anyway
+    // (extents of 72 in 32-wide slabs and chunks: abcd-aefb-fdce ran at 138 TFLOP/s direct, 415 after a
+    // transpose that fuses the ragged modes away)
+    const double tma_padding = double(u.tiles_m * u.BM) / double(p.Mtot) * double(u.tiles_n * u.BN) / double(p.Ntot) *
+                               double(u.k_iters * u.BK) / double(p.Ktot);
     if ((kernel == KERNEL_DMMA_F64_TMA || kernel == KERNEL_UMMA_TF32) && u.k_splits > 1) {
         // partial tensors written, read back and summed by a second kernel
         extra_us += c.launch_us + 2.0 * double(u.k_splits) * double(p.sizeC) * elt / (c.hbm_gbs * 1e3);
     }
     if (kernel == KERNEL_DMMA_F64_TMA) {
-        rate = c.dmma_f64_tflops * wave_efficiency(u.tiles_m * u.tiles_n * u.k_splits) / padded(u.BM, u.BN);
+        rate = c.dmma_f64_tflops * wave_efficiency(u.tiles_m * u.tiles_n * u.k_splits) / tma_padding;
         // Rows of a slab that are not contiguous in C are stored element by element
         // (abcdef-dega-gfbc: 37.7 M elements of C, 1.08 ms against 0.10 ms for its coalesced siblings).
         if (u.a.row_elem_cstride != 1) extra_us += double(p.sizeC) * double(u.k_splits) * c.scatter_store_ps * 1e-6;
@@ -552,9 +562,10 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
     }
     if (kernel == KERNEL_UMMA_TF32) {
         rate = c.umma_tf32_tflops * (1.0 - c.far_row_penalty * u.far_fraction) *
-               wave_efficiency((u.pair ? ceil_div(u.tiles_m, 2) : u.tiles_m) * u.tiles_n * u.k_splits);
-        // rows of a slab that are not contiguous in C cost a 32-byte sector per element
-        if (u.a.row_elem_cstride != 1) c_bytes *= 8.0;
+               wave_efficiency((u.pair ? ceil_div(u.tiles_m, 2) : u.tiles_m) * u.tiles_n * u.k_splits) / tma_padding;
+        // Rows of a slab that are not contiguous in C are stored element by element, a 32-byte sector each
+        // (abcd-dbea-ec, 9.0 M elements of C: 0.125 ms against a 0.022 ms traffic floor).
+        if (u.a.row_elem_cstride != 1) extra_us += double(p.sizeC) * double(u.k_splits) * c.scatter_store_f32_ps * 1e-6;
     }
     const double bytes = (double(p.sizeA) + double(p.sizeB)) * elt + c_bytes;
     return c.launch_us + std::max(flops / (rate * 1e6), bytes / (c.hbm_gbs * 1e3)) + extra_us;
@@ -578,8 +589,10 @@ int pick_kernel(const Problem& p, const UmmaSpec& u, const CostTable& c)
         if (us < best_us) best = KERNEL_DMMA_F64, best_us = us;
     }
     if (u.eligible && u.elt == 8) {
+        // The gather kernel's rates come from long contracted extents; on short ones it falls well below
+        // them (8 TFLOP/s at K = 24), so it has to look 30 % better than the TMA-fed kernel to be taken.
         const double us = contraction_us(p, KERNEL_DMMA_F64_TMA, u, c);
-        if (us < best_us) best = KERNEL_DMMA_F64_TMA, best_us = us;
+        if (us < (best == KERNEL_DMMA_F64 ? 1.3 : 1.0) * best_us) best = KERNEL_DMMA_F64_TMA, best_us = us;
     }
     return best;
 }
@@ -606,6 +619,7 @@ CostTable load_cost_table()
         else if (key == "dmma_f64_gather8_tflops") c.dmma_f64_gather8_tflops = v;
         else if (key == "dmma_f64_gather_narrow_tflops") c.dmma_f64_gather_narrow_tflops = v;
         else if (key == "scatter_store_ps") c.scatter_store_ps = v;
+        else if (key == "scatter_store_f32_ps") c.scatter_store_f32_ps = v;
         else if (key == "far_row_penalty") c.far_row_penalty = v;
     }
     return c;

@@ -109,6 +109,7 @@ struct CostTable {
     double dmma_f64_gather8_tflops = 12.0;  // gather tensor-path kernel, an operand on 8-byte gathers
     double dmma_f64_gather_narrow_tflops = 4.5;  // gather tensor-path kernel, 256 x 32 tiles (N <= 48)
     double scatter_store_ps = 28.0;         // per element of C stored on its own (TMA-fed FP64 kernel)
+    double scatter_store_f32_ps = 11.0;     // the same for the tcgen05 kernel's 4-byte elements
     double launch_us = 3.0;
     // Fraction of the tcgen05 rate lost per unit of staged bytes whose K rows lie 64 KB or more apart
     // (cfg5 on B200: 274 / 434 / 605 TFLOP/s with two thirds / one third / none of the bytes far-strided).
