@@ -71,15 +71,16 @@ __device__ __forceinline__ uint32_t step_k(uint32_t t, uint32_t fk) { return 8u 
 // Where a thread finds its fragments of one operand for one k:
 //   MN-major (rows of the stage are k, 16 consecutive m per row, slabs of 16 m `pitch` apart):
 //     one 16-byte load at  q0 + pair * pitch  holds fragments 2 pair and 2 pair + 1
-//   K-major (rows of the stage are m, 16 consecutive k per row):
-//     fragment i at  (i odd ? q1 : q0) + (i / 2) * 2048
-// Either way the 16-byte chunk index inside a 128-byte row is XORed with (row % 8).
+//   K-major (rows of the stage are m, BK consecutive k per row: 128 bytes, or 64 with a k chunk of 8):
+//     fragment i at  (i odd ? q1 : q0) + (i / 2) * pitch,  pitch = 16 rows
+// The 16-byte chunk index inside a row is XORed with (row % 8) (128-byte rows, 128-byte swizzle) or
+// with (row / 2) % 4 (64-byte rows, 64-byte swizzle).
 struct FragAddr {
     uint32_t q0, q1;
 };
 
 template <bool MN>
-__device__ __forceinline__ FragAddr frag_addr(uint32_t thread_base, uint32_t k, uint32_t fr)
+__device__ __forceinline__ FragAddr frag_addr(uint32_t thread_base, uint32_t k, uint32_t fr, bool rows64)
 {
     FragAddr f;
     if (MN) {
@@ -87,8 +88,13 @@ __device__ __forceinline__ FragAddr frag_addr(uint32_t thread_base, uint32_t k, 
         f.q1 = 0;
     } else {
         const uint32_t kk = (k & 1u) * 8u, kc = k >> 1;
-        f.q0 = thread_base + kk + ((kc ^ ((2u * fr) & 7u)) << 4);
-        f.q1 = thread_base + 128u + kk + ((kc ^ ((2u * fr + 1u) & 7u)) << 4);
+        if (rows64) {
+            f.q0 = thread_base + kk + ((kc ^ (fr & 3u)) << 4);  // rows 2 fr and 2 fr + 1 share (row / 2) % 4
+            f.q1 = f.q0 + 64u;
+        } else {
+            f.q0 = thread_base + kk + ((kc ^ ((2u * fr) & 7u)) << 4);
+            f.q1 = thread_base + 128u + kk + ((kc ^ ((2u * fr + 1u) & 7u)) << 4);
+        }
     }
     return f;
 }
@@ -102,7 +108,7 @@ __device__ __forceinline__ void load_all(double (&f)[N], const FragAddr& q, uint
         if (MN) {
             if ((i & 1) == 0) ld_shared_v2f64(q.q0 + static_cast<uint32_t>(i >> 1) * pitch, f[i], f[i + 1]);
         } else {
-            f[i] = ld_shared_f64(((i & 1) ? q.q1 : q.q0) + static_cast<uint32_t>(i >> 1) * 2048u);
+            f[i] = ld_shared_f64(((i & 1) ? q.q1 : q.q0) + static_cast<uint32_t>(i >> 1) * pitch);
         }
     }
 }
@@ -122,12 +128,12 @@ __device__ __forceinline__ void mma_step(double (&acc)[8][NF][2], const double (
             if (AMN) {
                 if ((i & 1) == 0) ld_shared_v2f64(qa.q0 + static_cast<uint32_t>(i >> 1) * a_pitch, an[i], an[i + 1]);
             } else {
-                an[i] = ld_shared_f64(((i & 1) ? qa.q1 : qa.q0) + static_cast<uint32_t>(i >> 1) * 2048u);
+                an[i] = ld_shared_f64(((i & 1) ? qa.q1 : qa.q0) + static_cast<uint32_t>(i >> 1) * a_pitch);
             }
             if (BMN) {
                 if ((i == 1 || i == 3) && i < NF) ld_shared_v2f64(qb.q0 + static_cast<uint32_t>(i >> 1) * b_pitch, bn[i - 1], bn[i]);
             } else {
-                if (i < NF) bn[i] = ld_shared_f64(((i & 1) ? qb.q1 : qb.q0) + static_cast<uint32_t>(i >> 1) * 2048u);
+                if (i < NF) bn[i] = ld_shared_f64(((i & 1) ? qb.q1 : qb.q0) + static_cast<uint32_t>(i >> 1) * b_pitch);
             }
         }
     }
@@ -297,10 +303,14 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         const int cw = warp & 3, grp = (warp >> 2) - 1, wm = cw & 1, wn = cw >> 1;
         const uint32_t fr = static_cast<uint32_t>(lane >> 2), fk = static_cast<uint32_t>(lane & 3);
         const uint32_t first = static_cast<uint32_t>(grp) * ring;
-        const uint32_t a_pitch = static_cast<uint32_t>(p.a.slab_bytes), b_pitch = static_cast<uint32_t>(p.b.slab_bytes);
-        const uint32_t a_thread = AMN ? static_cast<uint32_t>(wm * 4) * a_pitch : (static_cast<uint32_t>(wm * 64) + 2u * fr) * 128u;
+        // pitch between fragment pairs: one 16-wide slab (MN-major) or 16 rows (K-major)
+        const bool rows64 = p.BK == 8;
+        const uint32_t k_row = rows64 ? 64u : 128u;
+        const uint32_t a_pitch = AMN ? static_cast<uint32_t>(p.a.slab_bytes) : 16u * k_row;
+        const uint32_t b_pitch = BMN ? static_cast<uint32_t>(p.b.slab_bytes) : 16u * k_row;
+        const uint32_t a_thread = AMN ? static_cast<uint32_t>(wm * 4) * a_pitch : (static_cast<uint32_t>(wm * 64) + 2u * fr) * k_row;
         const uint32_t b_thread = a_tile_bytes + (BMN ? static_cast<uint32_t>(wn * (NF / 2)) * b_pitch
-                                                      : (static_cast<uint32_t>(wn * NF * 8) + 2u * fr) * 128u);
+                                                      : (static_cast<uint32_t>(wn * NF * 8) + 2u * fr) * k_row);
 
         double acc[8][NF][2];
 #pragma unroll
@@ -330,15 +340,15 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 if (ok) {
                     const uint32_t sb = smem_u32(smem) + ps * stage_bytes;
                     double fa0[8], fb0[NF], fa1[8], fb1[NF];
-                    FragAddr qa = frag_addr<AMN>(sb + a_thread, step_k(0, fk), fr), qb = frag_addr<BMN>(sb + b_thread, step_k(0, fk), fr);
+                    FragAddr qa = frag_addr<AMN>(sb + a_thread, step_k(0, fk), fr, rows64), qb = frag_addr<BMN>(sb + b_thread, step_k(0, fk), fr, rows64);
                     load_all<AMN, 8>(fa0, qa, a_pitch);
                     load_all<BMN, NF>(fb0, qb, b_pitch);
-                    qa = frag_addr<AMN>(sb + a_thread, step_k(1, fk), fr), qb = frag_addr<BMN>(sb + b_thread, step_k(1, fk), fr);
+                    qa = frag_addr<AMN>(sb + a_thread, step_k(1, fk), fr, rows64), qb = frag_addr<BMN>(sb + b_thread, step_k(1, fk), fr, rows64);
                     mma_step<true, AMN, BMN, NF>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
                     if (p.BK == 16) {
-                        qa = frag_addr<AMN>(sb + a_thread, step_k(2, fk), fr), qb = frag_addr<BMN>(sb + b_thread, step_k(2, fk), fr);
+                        qa = frag_addr<AMN>(sb + a_thread, step_k(2, fk), fr, rows64), qb = frag_addr<BMN>(sb + b_thread, step_k(2, fk), fr, rows64);
                         mma_step<true, AMN, BMN, NF>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
-                        qa = frag_addr<AMN>(sb + a_thread, step_k(3, fk), fr), qb = frag_addr<BMN>(sb + b_thread, step_k(3, fk), fr);
+                        qa = frag_addr<AMN>(sb + a_thread, step_k(3, fk), fr, rows64), qb = frag_addr<BMN>(sb + b_thread, step_k(3, fk), fr, rows64);
                         mma_step<true, AMN, BMN, NF>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
                     }
                     mma_step<false, AMN, BMN, NF>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);

@@ -216,7 +216,7 @@ bool stage_operand(const Problem& p, const std::vector<int>& t, const std::vecto
 void finish_operand(const Problem& p, const std::vector<int>& t, const std::vector<int>& rows, int tile_rows, int BK,
                     const std::vector<int>& kdigits, UmmaOperand* o, int max_slab_rows = 256)
 {
-    const int W = p.scalar_type == 1 ? 16 : 32;
+    const int elt = p.scalar_type == 1 ? 8 : 4, W = 128 / elt;
     if (o->major == 0) {
         // K-major: rows per slab = the largest power of two (8..tile height) that pads the slab
         // mode by at most 15 % (TF32, where fewer and larger TMA boxes matter more) or 3 % (FP64,
@@ -259,9 +259,9 @@ void finish_operand(const Problem& p, const std::vector<int>& t, const std::vect
         o->box[o->kc_dim] = BK;
         o->slab_bytes = BK * 128;
     } else {
-        o->box[o->kc_dim] = W;
+        o->box[o->kc_dim] = BK;  // = W except for FP64 with a k chunk of 8: 64-byte rows
         o->box[o->slab_dim] = o->slab_w;
-        o->slab_bytes = o->slab_w * 128;
+        o->slab_bytes = o->slab_w * BK * elt;
     }
     o->slabs_per_op = 1;
     o->digit0_scale = o->slab_w;
@@ -367,10 +367,10 @@ void plan_umma(const Problem& p, UmmaSpec* u)
     int BK = W;  // a K-major operand brings 128 bytes of K per row
     // Both operands MN-major: the k chunk may be narrower than a 128-byte row.  FP64 takes 8 instead of
     // 16 where that spares more than 15 % of zero-filled k (24 = 3 x 8 against 2 x 16).
-    if (!a_kmajor && !b_kmajor) {
-        if (f64) BK = kc_ext <= 8 || double(ceil_div(kc_ext, 16) * 16) > 1.15 * double(ceil_div(kc_ext, 8) * 8) ? 8 : 16;
-        else BK = kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32;
-    }
+    // (A K-major FP64 operand then has 64-byte rows under the 64-byte swizzle; the tcgen05 kernel keeps
+    // 128-byte rows for K-major operands.)
+    if (f64) BK = kc_ext <= 8 || double(ceil_div(kc_ext, 16) * 16) > 1.15 * double(ceil_div(kc_ext, 8) * 8) ? 8 : 16;
+    else if (!a_kmajor && !b_kmajor) BK = kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32;
     u->BK = BK;
     std::vector<int> kdigits{kc};
     for (int id : p.K)
@@ -393,11 +393,11 @@ void plan_umma(const Problem& p, UmmaSpec* u)
     // still yields at least one tile per SM; otherwise the narrowest admissible one.
     int bn = 32;
     if (f64) {
-        // the FP64 kernel has 128 x 64 and 128 x 32 tiles: the narrow one where it pads N less
+        // the FP64 kernel has 128 x 64 and 128 x 32 tiles: the narrow one where it pads N by over 15 % less
         UmmaOperand probe = u->b;
         finish_operand(p, p.B, p.N, 32, BK, kdigits, &probe);
         const int64_t padded = probe.total_slabs * probe.slab_w;
-        bn = ceil_div(padded, 32) * 32 < ceil_div(padded, 64) * 64 ? 32 : 64;
+        bn = double(ceil_div(padded, 32) * 32) * 1.15 < double(ceil_div(padded, 64) * 64) ? 32 : 64;
     } else {
         UmmaOperand probe = u->b;
         finish_operand(p, p.B, p.N, 32, BK, kdigits, &probe);

@@ -108,6 +108,9 @@ FP64_SHAPES = {
     "kmajor_long": Contraction("ab", "ka", "kb", dict(a=1537, b=1409, k=262), F64),                   # K-major boxes, ragged everywhere
     "scattered_store": Contraction("abc", "bda", "dc", dict(a=160, b=160, c=24, d=200), F64),          # slab mode b is not C's stride-1 mode
     "case21_like": Contraction("abcd", "aebf", "fdec", dict(a=72, b=24, c=24, d=72, e=24, f=16), F64),
+    "kmajor_k24": Contraction("ab", "ka", "kb", dict(a=1537, b=1409, k=24), F64),                      # k chunk of 8: 64-byte K-major rows
+    "mixed_k40": Contraction("ab", "ak", "kb", dict(a=1200, b=1000, k=40), F64),                       # the same with an MN-major A
+    "case33_like": Contraction("abcdef", "degc", "gfab", dict(a=24, b=16, c=16, d=24, e=16, f=16, g=24), F64),
     "long_k": Contraction("ab", "acd", "dbc", dict(a=312, b=296, c=40, d=36), F64),                  # 15 tiles, 108 k iterations: split-K
     "long_k_ragged": Contraction("ab", "ak", "kb", dict(a=200, b=120, k=1000), F64),
 }
@@ -131,7 +134,7 @@ def test_fp64_tensor_path(engine, oracle, monkeypatch, name, kernel):
     check(oracle, c, A, B, out, desc)
 
 
-@pytest.mark.parametrize("name", ["gemm_mn_k", "kmajor_long", "two_k_long"])
+@pytest.mark.parametrize("name", ["gemm_mn_k", "kmajor_long", "case21_like", "long_k_ragged"])
 def test_fp64_split_k_forced(engine, oracle, monkeypatch, name):
     monkeypatch.setenv("TCONT_SPLITK", "3")
     c = FP64_SHAPES[name]
