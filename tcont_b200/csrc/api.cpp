@@ -106,6 +106,20 @@ struct tcontb_run {
     std::vector<cudaEvent_t> shard_done;
     int first_device = 0;
     char split_mode = 0;
+    // Pipelined host-buffer pass (tcontb_run_contract_host): when C's slowest mode is external and is
+    // also the slowest mode of the operand that carries it, a slice of that mode is a contiguous range
+    // of the operand and of C.  The contraction is then cut into `parts` along it, each an ordinary
+    // run working in place on its ranges of this run's device buffers, so that the upload of slice
+    // i+1, the kernels of slice i and the download of slice i-1 overlap (PCIe is full duplex).
+    struct HostPipeline {
+        bool tried = false;
+        bool in_left = false;  // the caller's left operand carries the cut mode
+        size_t slice_in = 0, slice_out = 0;  // bytes per part
+        std::vector<std::unique_ptr<tcontb_run>> parts;
+        cudaStream_t s_in = nullptr, s_out = nullptr;
+        cudaEvent_t ev_start = nullptr, ev_other = nullptr;
+        std::vector<cudaEvent_t> ev_in, ev_done;
+    } pipe;
 
     ~tcontb_run()
     {
@@ -138,6 +152,13 @@ struct tcontb_run {
         }
         for (auto& e : ev)
             if (e) cudaEventDestroy(e);
+        pipe.parts.clear();
+        for (auto& e : pipe.ev_in) cudaEventDestroy(e);
+        for (auto& e : pipe.ev_done) cudaEventDestroy(e);
+        if (pipe.ev_start) cudaEventDestroy(pipe.ev_start);
+        if (pipe.ev_other) cudaEventDestroy(pipe.ev_other);
+        if (pipe.s_in) cudaStreamDestroy(pipe.s_in);
+        if (pipe.s_out) cudaStreamDestroy(pipe.s_out);
     }
     const void* roleA_src() const { return plan.prob.swapped ? dR : dL; }
     const void* roleB_src() const { return plan.prob.swapped ? dL : dR; }
@@ -458,6 +479,71 @@ tcontb_status make_shards(tcontb_run* run, int gpus)
     return TCONTB_OK;
 }
 
+// Builds the parts of the pipelined host-buffer pass, if the descriptor allows it (see HostPipeline).
+// TCONT_HOST_CHUNKS=<n> forces the number of parts (0 or 1: one pass, no overlap).
+tcontb_status build_host_pipeline(tcontb_run* run)
+{
+    auto& pp = run->pipe;
+    pp.tried = true;
+    const Plan& pl = run->plan;
+    if (!run->shards.empty() || pl.modeC.empty()) return TCONTB_OK;
+    const char mode = pl.modeC.back();
+    const bool left = pl.modeA.find(mode) != std::string::npos, right = pl.modeB.find(mode) != std::string::npos;
+    if (left == right) return TCONTB_OK;
+    const std::string& carrier = left ? pl.modeA : pl.modeB;
+    if (carrier.back() != mode) return TCONTB_OK;
+    const int64_t ext = pl.ext_val[pl.ext_mode.find(mode)];
+    const size_t in_bytes = static_cast<size_t>(left ? pl.sizeL : pl.sizeR) * run->elt, out_bytes = static_cast<size_t>(pl.sizeC) * run->elt;
+    int64_t n = 0;
+    if (const char* e = std::getenv("TCONT_HOST_CHUNKS")) {
+        n = std::atoll(e);
+        if (n < 2 || ext % n) return TCONTB_OK;
+    } else {
+        // as many parts as leave 16 MB of C per part, 8 at most
+        for (int64_t c : {8, 6, 4, 3, 2})
+            if (!n && ext % c == 0 && out_bytes / static_cast<size_t>(c) >= (size_t(16) << 20)) n = c;
+        if (!n) return TCONTB_OK;
+    }
+    pp.slice_in = in_bytes / static_cast<size_t>(n);
+    pp.slice_out = out_bytes / static_cast<size_t>(n);
+    if (pp.slice_in % 16 || pp.slice_out % 16) return TCONTB_OK;
+    std::vector<int64_t> local_ext = pl.ext_val;
+    local_ext[pl.ext_mode.find(mode)] = ext / n;
+    std::vector<std::unique_ptr<tcontb_run>> parts;
+    for (int64_t i = 0; i < n; ++i) {
+        std::unique_ptr<tcontb_run> part(new tcontb_run());
+        std::string err;
+        const int rc = make_plan(pl.modeC.data(), static_cast<int>(pl.modeC.size()), pl.modeA.data(), static_cast<int>(pl.modeA.size()),
+                                 pl.modeB.data(), static_cast<int>(pl.modeB.size()), pl.op, pl.scalar_type, pl.ext_mode.data(),
+                                 local_ext.data(), static_cast<int>(local_ext.size()), pl.backend_selection, load_cost_table(),
+                                 &part->plan, &err);
+        if (rc) return fail(static_cast<tcontb_status>(rc), err);
+        part->elt = run->elt;
+        part->stream = run->stream;
+        unsigned char* in = static_cast<unsigned char*>(left ? run->dL : run->dR) + static_cast<size_t>(i) * pp.slice_in;
+        part->dL = left ? static_cast<void*>(in) : run->dL;
+        part->dR = left ? run->dR : static_cast<void*>(in);
+        part->dC = static_cast<unsigned char*>(run->dC) + static_cast<size_t>(i) * pp.slice_out;
+        const tcontb_status st = finish_run(part.get());
+        if (st != TCONTB_OK) return st;
+        parts.push_back(std::move(part));
+    }
+    TC_CUDA(cudaStreamCreateWithFlags(&pp.s_in, cudaStreamNonBlocking));
+    TC_CUDA(cudaStreamCreateWithFlags(&pp.s_out, cudaStreamNonBlocking));
+    TC_CUDA(cudaEventCreateWithFlags(&pp.ev_start, cudaEventDisableTiming));
+    TC_CUDA(cudaEventCreateWithFlags(&pp.ev_other, cudaEventDisableTiming));
+    for (int64_t i = 0; i < n; ++i) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        TC_CUDA(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        pp.ev_in.push_back(a);
+        TC_CUDA(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+        pp.ev_done.push_back(b);
+    }
+    pp.in_left = left;
+    pp.parts = std::move(parts);
+    return TCONTB_OK;
+}
+
 #define TC_NOT_SHARDED(run, what)                                                                              \
     if (!(run)->shards.empty()) return fail(TCONTB_UNSUPPORTED, what " is not available on a multi-GPU run")
 
@@ -582,6 +668,7 @@ tcontb_status tcontb_run_set_stream(tcontb_run* run, void* cuda_stream)
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
     TC_NOT_SHARDED(run, "a caller stream");
     run->stream = static_cast<cudaStream_t>(cuda_stream);
+    for (auto& part : run->pipe.parts) part->stream = run->stream;
     return TCONTB_OK;
 }
 
@@ -751,6 +838,44 @@ tcontb_status tcontb_run_contract_host(tcontb_run* run, const void* a_host, cons
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
     if (!c_host) return fail(TCONTB_INVALID_ARGUMENT, "Destination buffer is null");
     TC_NOT_SHARDED(run, "the host-buffer pass");
+    if (!a_host || !b_host) return fail(TCONTB_INVALID_ARGUMENT, "Null input buffer");
+    if (!run->pipe.tried) {
+        const tcontb_status bs = build_host_pipeline(run);
+        if (bs != TCONTB_OK) return bs;
+    }
+    if (!run->pipe.parts.empty()) {
+        auto& pp = run->pipe;
+        const Plan& pl = run->plan;
+        const size_t n = pp.parts.size();
+        const unsigned char* cut_host = static_cast<const unsigned char*>(pp.in_left ? a_host : b_host);
+        unsigned char* cut_dev = static_cast<unsigned char*>(pp.in_left ? run->dL : run->dR);
+        // uploads start once everything queued on the run's stream so far is done with the buffers
+        TC_CUDA(cudaEventRecord(pp.ev_start, run->stream));
+        TC_CUDA(cudaStreamWaitEvent(pp.s_in, pp.ev_start, 0));
+        TC_CUDA(cudaStreamWaitEvent(pp.s_out, pp.ev_start, 0));
+        if (pp.in_left) TC_CUDA(cudaMemcpyAsync(run->dR, b_host, static_cast<size_t>(pl.sizeR) * run->elt, cudaMemcpyHostToDevice, pp.s_in));
+        else TC_CUDA(cudaMemcpyAsync(run->dL, a_host, static_cast<size_t>(pl.sizeL) * run->elt, cudaMemcpyHostToDevice, pp.s_in));
+        TC_CUDA(cudaEventRecord(pp.ev_other, pp.s_in));
+        for (size_t i = 0; i < n; ++i) {
+            TC_CUDA(cudaMemcpyAsync(cut_dev + i * pp.slice_in, cut_host + i * pp.slice_in, pp.slice_in, cudaMemcpyHostToDevice, pp.s_in));
+            TC_CUDA(cudaEventRecord(pp.ev_in[i], pp.s_in));
+        }
+        TC_CUDA(cudaStreamWaitEvent(run->stream, pp.ev_other, 0));
+        for (size_t i = 0; i < n; ++i) {
+            TC_CUDA(cudaStreamWaitEvent(run->stream, pp.ev_in[i], 0));
+            const tcontb_status ls = tcontb_run_launch(pp.parts[i].get());
+            if (ls != TCONTB_OK) return ls;
+            TC_CUDA(cudaEventRecord(pp.ev_done[i], run->stream));
+            TC_CUDA(cudaStreamWaitEvent(pp.s_out, pp.ev_done[i], 0));
+            TC_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(c_host) + i * pp.slice_out, static_cast<unsigned char*>(run->dC) + i * pp.slice_out,
+                                    pp.slice_out, cudaMemcpyDeviceToHost, pp.s_out));
+        }
+        TC_CUDA(cudaStreamSynchronize(pp.s_out));
+        TC_CUDA(cudaStreamSynchronize(run->stream));
+        if (h2d) *h2d = (pl.sizeL + pl.sizeR) * static_cast<int64_t>(run->elt);
+        if (d2h) *d2h = static_cast<int64_t>(pl.sizeC) * static_cast<int64_t>(run->elt);
+        return TCONTB_OK;
+    }
     tcontb_status st = tcontb_run_upload_inputs(run, a_host, b_host);
     if (st != TCONTB_OK) return st;
     st = tcontb_run_launch(run);
@@ -780,6 +905,12 @@ tcontb_status tcontb_run_device_status(tcontb_run* run, int* status)
     }
     TC_CUDA(cudaMemcpyAsync(status, run->status.ptr, sizeof(int), cudaMemcpyDeviceToHost, run->stream));
     TC_CUDA(cudaStreamSynchronize(run->stream));
+    for (auto& part : run->pipe.parts) {
+        int s1 = 0;
+        const tcontb_status st = tcontb_run_device_status(part.get(), &s1);
+        if (st != TCONTB_OK) return st;
+        if (s1 > *status) *status = s1;
+    }
     return TCONTB_OK;
 }
 

@@ -250,12 +250,23 @@ def test_generated_inputs_roundtrip(engine, oracle, monkeypatch):
     assert engine.stage_times(r)["available"] is False
 
 
-def test_host_buffer_path(engine, oracle):
-    c = Contraction("abc", "adc", "db", dict(a=64, c=4, b=96, d=64), F32)
+@pytest.mark.parametrize("chunks", ["1", "2", "4"])
+@pytest.mark.parametrize("c", [
+    Contraction("abc", "adc", "db", dict(a=64, c=4, b=96, d=64), F32),          # C's slowest mode c is A's slowest: pipelined in parts
+    Contraction("abcd", "ea", "ebcd", dict(a=40, b=6, c=5, d=8, e=24), F64),    # ... d is the right operand's slowest mode
+    Contraction("abcde", "efba", "cfd", dict(a=12, b=8, c=16, d=6, e=8, f=8), F32),  # e is A's stride-1 mode: one pass
+], ids=["left", "right", "strided"])
+def test_host_buffer_path(engine, oracle, monkeypatch, c, chunks):
+    """tcontb_run_contract_host: upload, contraction and download, cut into overlapping parts where slices are contiguous."""
+    monkeypatch.setenv("TCONT_HOST_CHUNKS", chunks)
     A, B = oracle.inputs(c, 1, -1.0, 1.0)
     p = engine.plan(to_equation(engine, c))
     r = engine.prepare(p, np.zeros_like(A), np.zeros_like(B))
-    out = np.empty(c.size(c.modeC), dtype=np.float32)
-    h2d, d2h = r.contract_host(A, B, out)
-    assert h2d == A.nbytes + B.nbytes and d2h == out.nbytes
-    check(oracle, c, A, B, out, p.describe())
+    out = np.full(c.size(c.modeC), np.nan, dtype=A.dtype)
+    for _ in range(2):   # the second call reuses the parts built by the first
+        out.fill(np.nan)
+        h2d, d2h = r.contract_host(A, B, out)
+        assert h2d == A.nbytes + B.nbytes and d2h == out.nbytes
+        check(oracle, c, A, B, out, p.describe())
+    assert r.device_status() == 0
+    np.testing.assert_array_equal(engine.copy_output_to_host(r), out)   # the device copy of C is whole as well
