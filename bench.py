@@ -292,6 +292,15 @@ def main():
     if contracted:
         nccl_bytes = (world - 1) / world * nC * (8 if st else 4)   # leaves each GPU in the reduce-scatter
 
+    # spread of single launches (the reference's per-iteration harness reports min and stddev,
+    # benchmarks/test/tccg/bench_tccg_iter.cpp:218-233); outside the timed region
+    launch_stats = None
+    if not contracted:
+        one = [run.time_launches(1)[0] for _ in range(min(20, max(args.steps, 1)))]
+        mean = sum(one) / len(one)
+        launch_stats = {"n": len(one), "min_ms": min(one), "mean_ms": mean,
+                        "std_ms": (sum((x - mean) ** 2 for x in one) / len(one)) ** 0.5}
+
     # end to end through the host-buffer entry point: pinned host A, B -> device, launch, C -> pinned host
     hA = torch.from_numpy(A).pin_memory()
     hB = torch.from_numpy(B).pin_memory()
@@ -350,7 +359,7 @@ def main():
                            "sharded_mode": shard_mode, "split": args.split, "backend": desc["backend"], "kernel": desc["kernel"],
                            "l2": "inputs and output exceed the 126 MB L2" if alg_bytes > 126e6 else "working set fits L2",
                            "timing": "CUDA events on the launching stream, max over ranks"},
-                "clocks": clocks, "gpu_launches": int(launches),
+                "clocks": clocks, "gpu_launches": int(launches), "launch_stats": launch_stats,
                 "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                         "ms_per_step": e2e_ms, "checksum": checksum},
                 "roofline": roofline}

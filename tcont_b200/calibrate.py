@@ -79,14 +79,17 @@ def calibrate() -> dict:
                                                       env={"TCONT_KERNEL": "gather"})
     assert k == "dmma_f64", k
     table["simt_f64_tflops"], _ = _rate(tc, api, torch, ("ab", "ak", "bk"), dict(a=4096, b=4096, k=1024), F64, env={"TCONT_KERNEL": "simt"})
-    # scattered stores of the TMA-fed FP64 kernel: two contractions of the same size, one whose tile rows
-    # run along C's stride-1 mode and one whose rows do not; the difference per element of C
-    ext = dict(a=312, b=312, c=24, d=312)
-    t_rows, k1 = _rate(tc, api, torch, ("abc", "dca", "bd"), dict(a=312, b=24, c=312, d=312), F64)
-    t_scat, k2 = _rate(tc, api, torch, ("abc", "bda", "dc"), ext, F64)
-    if k1 == k2 == "dmma_f64_tma":
-        flops = 2.0 * 312 * 312 * 24 * 312
-        table["scatter_store_ps"] = max(0.0, (flops / (t_scat * 1e12) - flops / (t_rows * 1e12)) / (312 * 312 * 24) * 1e12)
+    # scattered stores of the TMA-fed kernels: two contractions of the same size with a short contracted
+    # extent, one whose tile rows run along C's stride-1 mode and one whose rows do not (every element of C
+    # stored on its own); the time of the second per element of C
+    ext6 = dict(a=24, b=16, c=16, d=24, e=16, f=16, g=24)
+    size_c = 24 * 16 * 16 * 24 * 16 * 16
+    flops6 = 2.0 * size_c * 24
+    for key, scalar in (("scatter_store_ps", F64), ("scatter_store_f32_ps", F32)):
+        _, k1 = _rate(tc, api, torch, ("abcdef", "degb", "gfac"), ext6, scalar)
+        t_scat, k2 = _rate(tc, api, torch, ("abcdef", "dega", "gfbc"), ext6, scalar)
+        if k1 == k2 and k1 in ("dmma_f64_tma", "umma_tf32"):
+            table[key] = flops6 / (t_scat * 1e12) / size_c * 1e12
     # far-row penalty: the same 4-D contraction with the chunked contracted mode near (f) and far (e) in B
     shape = (("abcd", "aebf", "cfde"), dict(a=128, b=128, c=128, d=128, e=64, f=64))
     near, _ = _rate(tc, api, torch, *shape, F32, iters=3, env={"TCONT_UMMA_KC": "f"})

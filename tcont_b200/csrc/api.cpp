@@ -203,9 +203,9 @@ tcontb_status encode_map(const UmmaOperand& o, const void* base, int elt, CUtens
     const CUresult r = fn(out, elt == 8 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT64 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, kMaxTmaRank, const_cast<void*>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE,
                           // an MN-major 32-bit operand must be swizzled in 32-byte units for tcgen05.mma;
-                          // a K-major FP64 operand with a k chunk of 8 has 64-byte rows
+                          // FP64 operands may have 64-byte rows (8 doubles of the k chunk or of the slab mode)
                           (o.major && elt == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
-                          : (!o.major && o.box[o.kc_dim] * elt == 64) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          : (o.box[0] * elt == 64) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TCONTB_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));

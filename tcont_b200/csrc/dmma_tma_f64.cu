@@ -69,7 +69,8 @@ __device__ __forceinline__ void st_global_cs_v4f64(double* p, double a, double b
 __device__ __forceinline__ uint32_t step_k(uint32_t t, uint32_t fk) { return 8u * (t >> 1) + 2u * fk + ((fk ^ t) & 1u); }
 
 // Where a thread finds its fragments of one operand for one k:
-//   MN-major (rows of the stage are k, 16 consecutive m per row, slabs of 16 m `pitch` apart):
+//   MN-major (rows of the stage are k, 16 consecutive m per 128-byte row, slabs of 16 m one slab apart;
+//   or 8 m per 64-byte row, two slabs per 16 m):
 //     one 16-byte load at  q0 + pair * pitch  holds fragments 2 pair and 2 pair + 1
 //   K-major (rows of the stage are m, BK consecutive k per row: 128 bytes, or 64 with a k chunk of 8):
 //     fragment i at  (i odd ? q1 : q0) + (i / 2) * pitch,  pitch = 16 rows
@@ -79,12 +80,14 @@ struct FragAddr {
     uint32_t q0, q1;
 };
 
+// `rows64`: K-major rows of 64 bytes (k chunk of 8); `slabs8`: MN-major rows of 64 bytes (slabs of 8)
 template <bool MN>
-__device__ __forceinline__ FragAddr frag_addr(uint32_t thread_base, uint32_t k, uint32_t fr, bool rows64)
+__device__ __forceinline__ FragAddr frag_addr(uint32_t thread_base, uint32_t k, uint32_t fr, bool rows64, bool slabs8)
 {
     FragAddr f;
     if (MN) {
-        f.q0 = thread_base + k * 128u + ((fr ^ (k & 7u)) << 4);
+        // (with slabs of 8 the thread's slab, fr / 4, is already part of thread_base)
+        f.q0 = slabs8 ? thread_base + k * 64u + (((fr & 3u) ^ ((k >> 1) & 3u)) << 4) : thread_base + k * 128u + ((fr ^ (k & 7u)) << 4);
         f.q1 = 0;
     } else {
         const uint32_t kk = (k & 1u) * 8u, kc = k >> 1;
@@ -306,10 +309,12 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         // pitch between fragment pairs: one 16-wide slab (MN-major) or 16 rows (K-major)
         const bool rows64 = p.BK == 8;
         const uint32_t k_row = rows64 ? 64u : 128u;
-        const uint32_t a_pitch = AMN ? static_cast<uint32_t>(p.a.slab_bytes) : 16u * k_row;
-        const uint32_t b_pitch = BMN ? static_cast<uint32_t>(p.b.slab_bytes) : 16u * k_row;
-        const uint32_t a_thread = AMN ? static_cast<uint32_t>(wm * 4) * a_pitch : (static_cast<uint32_t>(wm * 64) + 2u * fr) * k_row;
-        const uint32_t b_thread = a_tile_bytes + (BMN ? static_cast<uint32_t>(wn * (NF / 2)) * b_pitch
+        const bool a8 = AMN && p.a.slab_w == 8, b8 = BMN && p.b.slab_w == 8;  // 16 m = two slabs of 8
+        const uint32_t a_pitch = AMN ? static_cast<uint32_t>(p.a.slab_bytes) * (a8 ? 2u : 1u) : 16u * k_row;
+        const uint32_t b_pitch = BMN ? static_cast<uint32_t>(p.b.slab_bytes) * (b8 ? 2u : 1u) : 16u * k_row;
+        const uint32_t a_thread = AMN ? static_cast<uint32_t>(wm * 4) * a_pitch + (a8 ? (fr >> 2) * static_cast<uint32_t>(p.a.slab_bytes) : 0u)
+                                      : (static_cast<uint32_t>(wm * 64) + 2u * fr) * k_row;
+        const uint32_t b_thread = a_tile_bytes + (BMN ? static_cast<uint32_t>(wn * (NF / 2)) * b_pitch + (b8 ? (fr >> 2) * static_cast<uint32_t>(p.b.slab_bytes) : 0u)
                                                       : (static_cast<uint32_t>(wn * NF * 8) + 2u * fr) * k_row);
 
         double acc[8][NF][2];
@@ -330,35 +335,55 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             const WorkUnit w = decode_unit(blockIdx.x + i * gridDim.x, p, tiles_m, tiles_n);
             double* __restrict__ C = p.C64 + static_cast<long long>(w.split) * p.split_stride;
             bool tile_ok = true;
+            // fa0/fb0 may already hold the first fragments of the stage about to be worked on: the last step
+            // of a stage fetches them when the next stage has landed by then, instead of ending with a
+            // step without loads and starting the next stage with loads nothing overlaps
+            bool have_first = false;
+            double fa0[8], fb0[NF], fa1[8], fb1[NF];
             for (int it = 0; it < w.n_it; ++it) {
                 if (i == 0 && my_tiles > 1 && it == w.n_it / 2) asm volatile("bar.arrive 1, 256;" ::: "memory");
                 const uint32_t ps = first + stage;
-                const long long tw = prof ? clock64() : 0;
-                const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_full + ps), phase, abort_flag));
-                if (prof) t_full += clock64() - tw;
+                bool ok = true;
+                if (!have_first) {
+                    const long long tw = prof ? clock64() : 0;
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_full + ps), phase, abort_flag));
+                    if (prof) t_full += clock64() - tw;
+                }
                 tile_ok = tile_ok && ok;
+                const uint32_t next_stage = stage + 1 == ring ? 0u : stage + 1u, next_phase = stage + 1 == ring ? phase ^ 1u : phase;
+                bool next_first = false;
                 if (ok) {
                     const uint32_t sb = smem_u32(smem) + ps * stage_bytes;
-                    double fa0[8], fb0[NF], fa1[8], fb1[NF];
-                    FragAddr qa = frag_addr<AMN>(sb + a_thread, step_k(0, fk), fr, rows64), qb = frag_addr<BMN>(sb + b_thread, step_k(0, fk), fr, rows64);
-                    load_all<AMN, 8>(fa0, qa, a_pitch);
-                    load_all<BMN, NF>(fb0, qb, b_pitch);
-                    qa = frag_addr<AMN>(sb + a_thread, step_k(1, fk), fr, rows64), qb = frag_addr<BMN>(sb + b_thread, step_k(1, fk), fr, rows64);
+                    FragAddr qa, qb;
+                    if (!have_first) {
+                        qa = frag_addr<AMN>(sb + a_thread, step_k(0, fk), fr, rows64, a8), qb = frag_addr<BMN>(sb + b_thread, step_k(0, fk), fr, rows64, b8);
+                        load_all<AMN, 8>(fa0, qa, a_pitch);
+                        load_all<BMN, NF>(fb0, qb, b_pitch);
+                    }
+                    qa = frag_addr<AMN>(sb + a_thread, step_k(1, fk), fr, rows64, a8), qb = frag_addr<BMN>(sb + b_thread, step_k(1, fk), fr, rows64, b8);
                     mma_step<true, AMN, BMN, NF>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
                     if (p.BK == 16) {
-                        qa = frag_addr<AMN>(sb + a_thread, step_k(2, fk), fr, rows64), qb = frag_addr<BMN>(sb + b_thread, step_k(2, fk), fr, rows64);
+                        qa = frag_addr<AMN>(sb + a_thread, step_k(2, fk), fr, rows64, a8), qb = frag_addr<BMN>(sb + b_thread, step_k(2, fk), fr, rows64, b8);
                         mma_step<true, AMN, BMN, NF>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
-                        qa = frag_addr<AMN>(sb + a_thread, step_k(3, fk), fr, rows64), qb = frag_addr<BMN>(sb + b_thread, step_k(3, fk), fr, rows64);
+                        qa = frag_addr<AMN>(sb + a_thread, step_k(3, fk), fr, rows64, a8), qb = frag_addr<BMN>(sb + b_thread, step_k(3, fk), fr, rows64, b8);
                         mma_step<true, AMN, BMN, NF>(acc, fa0, fb0, fa1, fb1, qa, qb, a_pitch, b_pitch);
                     }
-                    mma_step<false, AMN, BMN, NF>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
+                    // last step: one look at the next stage's barrier; if its data is there, fetch from it
+                    if (it + 1 < w.n_it)
+                        next_first = __all_sync(0xffffffffu, mbar_try_wait(smem_u32(bar_full + first + next_stage), next_phase));
+                    if (next_first) {
+                        const uint32_t nb = smem_u32(smem) + (first + next_stage) * stage_bytes;
+                        qa = frag_addr<AMN>(nb + a_thread, step_k(0, fk), fr, rows64, a8), qb = frag_addr<BMN>(nb + b_thread, step_k(0, fk), fr, rows64, b8);
+                        mma_step<true, AMN, BMN, NF>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
+                    } else {
+                        mma_step<false, AMN, BMN, NF>(acc, fa1, fb1, fa0, fb0, qa, qb, a_pitch, b_pitch);
+                    }
                 }
+                have_first = next_first;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(bar_empty + ps));  // this warp is done reading the stage
-                if (++stage == ring) {
-                    stage = 0;
-                    phase ^= 1u;
-                }
+                stage = next_stage;
+                phase = next_phase;
             }
             if (prof) { const long long t1 = clock64(); t_main += t1 - t0; t0 = t1; }
 

@@ -196,6 +196,10 @@ bool stage_operand(const Problem& p, const std::vector<int>& t, const std::vecto
     if (o->major == 1) {
         slab_mode = first;
         o->slab_w = W;
+        // FP64: slabs of 8 doubles (64-byte rows, 64-byte swizzle) where 16 would pad the mode by over 8 %
+        // (extent 72: 5 x 16 = 80 against 9 x 8)
+        const int64_t e = p.modes[static_cast<size_t>(first)].extent;
+        if (elt == 8 && double(ceil_div(e, 16) * 16) > 1.08 * double(ceil_div(e, 8) * 8)) o->slab_w = 8;
     } else {
         if (first != kc_mode) {
             *why = "K-major operand whose stride-1 mode is not the chunked K mode";
@@ -255,9 +259,9 @@ void finish_operand(const Problem& p, const std::vector<int>& t, const std::vect
     for (int i = 0; i < 3; ++i)
         o->k_digit_dim[i] = i < static_cast<int>(kdigits.size()) ? index_of(t, kdigits[static_cast<size_t>(i)]) : -1;
     if (o->major == 1) {
-        o->box[o->slab_dim] = W;
+        o->box[o->slab_dim] = o->slab_w;
         o->box[o->kc_dim] = BK;
-        o->slab_bytes = BK * 128;
+        o->slab_bytes = BK * o->slab_w * elt;
     } else {
         o->box[o->kc_dim] = BK;  // = W except for FP64 with a k chunk of 8: 64-byte rows
         o->box[o->slab_dim] = o->slab_w;
@@ -265,7 +269,7 @@ void finish_operand(const Problem& p, const std::vector<int>& t, const std::vect
     }
     o->slabs_per_op = 1;
     o->digit0_scale = o->slab_w;
-    o->oob_coord = static_cast<int>(ceil_div(o->slab_mode_ext, W) * W);
+    o->oob_coord = static_cast<int>(ceil_div(o->slab_mode_ext, W) * W);  // (any coordinate past the mode's end)
 }
 
 // Merged boxes for an MN-major operand: the slab mode (stride-1, extent a multiple of 32) is
@@ -529,7 +533,7 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
     const double flops = 2.0 * double(p.Mtot) * double(p.Ntot) * double(p.Ktot);
     double c_bytes = double(p.sizeC) * elt;
     double rate = p.scalar_type == 1 ? c.simt_f64_tflops : c.simt_f32_tflops;
-    double extra_us = 0;
+    double extra_us = 0, scatter_us = 0;
     // tiles are computed whole: the work of an FP64 kernel is that of the extents rounded up to its tile
     auto padded = [&](int64_t bm, int64_t bn) {
         return double(ceil_div(p.Mtot, bm) * bm) / double(p.Mtot) * double(ceil_div(p.Ntot, bn) * bn) / double(p.Ntot);
@@ -549,7 +553,7 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
         rate = c.dmma_f64_tflops * wave_efficiency(u.tiles_m * u.tiles_n * u.k_splits) / tma_padding;
         // Rows of a slab that are not contiguous in C are stored element by element
         // (abcdef-dega-gfbc: 37.7 M elements of C, 1.08 ms against 0.10 ms for its coalesced siblings).
-        if (u.a.row_elem_cstride != 1) extra_us += double(p.sizeC) * double(u.k_splits) * c.scatter_store_ps * 1e-6;
+        if (u.a.row_elem_cstride != 1) scatter_us = double(p.sizeC) * double(u.k_splits) * c.scatter_store_ps * 1e-6;
     }
     if (kernel == KERNEL_DMMA_F64) {
         const int64_t bn = p.Ntot <= 48 ? 32 : 64, bm = p.Ntot <= 48 ? 256 : 128;
@@ -565,10 +569,12 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
                wave_efficiency((u.pair ? ceil_div(u.tiles_m, 2) : u.tiles_m) * u.tiles_n * u.k_splits) / tma_padding;
         // Rows of a slab that are not contiguous in C are stored element by element, a 32-byte sector each
         // (abcd-dbea-ec, 9.0 M elements of C: 0.125 ms against a 0.022 ms traffic floor).
-        if (u.a.row_elem_cstride != 1) extra_us += double(p.sizeC) * double(u.k_splits) * c.scatter_store_f32_ps * 1e-6;
+        if (u.a.row_elem_cstride != 1) scatter_us = double(p.sizeC) * double(u.k_splits) * c.scatter_store_f32_ps * 1e-6;
     }
     const double bytes = (double(p.sizeA) + double(p.sizeB)) * elt + c_bytes;
-    return c.launch_us + std::max(flops / (rate * 1e6), bytes / (c.hbm_gbs * 1e3)) + extra_us;
+    // scattered stores are a third ceiling rather than an addition: one consumer group stores while the
+    // other computes (abc-bda-dc, K = 312: 0.086 ms scattered against 0.072 ms for its coalesced sibling)
+    return c.launch_us + std::max({flops / (rate * 1e6), bytes / (c.hbm_gbs * 1e3), scatter_us}) + extra_us;
 }
 
 // TF32 goes to the tcgen05 kernel whenever its tiles can be described to TMA.  FP64 takes the

@@ -108,6 +108,8 @@ FP64_SHAPES = {
     "kmajor_long": Contraction("ab", "ka", "kb", dict(a=1537, b=1409, k=262), F64),                   # K-major boxes, ragged everywhere
     "scattered_store": Contraction("abc", "bda", "dc", dict(a=160, b=160, c=24, d=200), F64),          # slab mode b is not C's stride-1 mode
     "case21_like": Contraction("abcd", "aebf", "fdec", dict(a=72, b=24, c=24, d=72, e=24, f=16), F64),
+    "case20_like": Contraction("abcd", "aebf", "dfce", dict(a=72, b=24, c=24, d=72, e=24, f=16), F64),   # both MN-major on extents of 72: slabs of 8
+    "slab8_k8": Contraction("abcd", "aebf", "dfce", dict(a=40, b=60, c=40, d=24, e=24, f=3), F64),        # slabs of 8 with a k chunk of 8 (f = 3: mostly zero fill)
     "kmajor_k24": Contraction("ab", "ka", "kb", dict(a=1537, b=1409, k=24), F64),                      # k chunk of 8: 64-byte K-major rows
     "mixed_k40": Contraction("ab", "ak", "kb", dict(a=1200, b=1000, k=40), F64),                       # the same with an MN-major A
     "case33_like": Contraction("abcdef", "degc", "gfab", dict(a=24, b=16, c=16, d=24, e=16, f=16, g=24), F64),
