@@ -499,8 +499,9 @@ tcontb_status build_host_pipeline(tcontb_run* run)
         n = std::atoll(e);
         if (n < 2 || ext % n) return TCONTB_OK;
     } else {
-        // as many parts as leave 16 MB of C per part, 8 at most
-        for (int64_t c : {8, 6, 4, 3, 2})
+        // as many parts as leave 16 MB of C per part, 16 at most (the first upload and the last download
+        // are the only transfers nothing overlaps)
+        for (int64_t c : {16, 12, 8, 6, 4, 3, 2})
             if (!n && ext % c == 0 && out_bytes / static_cast<size_t>(c) >= (size_t(16) << 20)) n = c;
         if (!n) return TCONTB_OK;
     }
