@@ -62,11 +62,13 @@ __device__ __forceinline__ void st_global_cs_v4f64(double* p, double a, double b
     asm volatile("st.global.cs.v4.f64 [%0], {%1, %2, %3, %4};" ::"l"(p), "d"(a), "d"(b), "d"(c), "d"(d) : "memory");
 }
 
-// Which k a lane feeds into step t of a stage: k = 8 (t / 2) + 2 fk + ((fk ^ t) & 1), fk = lane % 4.
-// Any assignment works as long as both operands use the same one; with this one the four rows an
-// MN-major 16-byte load touches per quarter warp differ in k / 2, which after the XOR swizzle puts
-// the quarter's eight 16-byte chunks into eight different bank groups.
-__device__ __forceinline__ uint32_t step_k(uint32_t t, uint32_t fk) { return 8u * (t >> 1) + 2u * fk + ((fk ^ t) & 1u); }
+// Which k a lane feeds into step t of a stage: k = 8 (t / 2) + 2 fk + ((fk ^ (fk >> 1) ^ t) & 1), fk = lane % 4.
+// Any assignment works as long as both operands use the same one.  With this one
+//  * the four rows an MN-major 16-byte load touches per quarter warp differ in k / 2, which after the
+//    XOR swizzle puts the quarter's eight 16-byte chunks into eight different bank groups;
+//  * the two lanes of a half warp that meet in the same 16-byte chunk of a K-major operand (rows
+//    2 fr + par with fr two apart in the swizzle) take different halves of it.
+__device__ __forceinline__ uint32_t step_k(uint32_t t, uint32_t fk) { return 8u * (t >> 1) + 2u * fk + ((fk ^ (fk >> 1) ^ t) & 1u); }
 
 // Where a thread finds its fragments of one operand for one k:
 //   MN-major (rows of the stage are k, 16 consecutive m per 128-byte row, slabs of 16 m one slab apart;

@@ -85,6 +85,29 @@ def test_fp64_kernel_choice_follows_the_cost_table(engine, monkeypatch):
     assert describe(engine, CONFIGS["cfg1"][0])["kernel"] in ("simt", "dmma_f64_tma")
 
 
+def test_fp64_row_widths_and_split_k(engine, monkeypatch):
+    F64 = 1
+    # extents of 72: slabs of 8 doubles (9 x 8) instead of 16 (5 x 16, 11 % padding) for the MN-major A,
+    # 8 rows per slab for the K-major B
+    d = describe(engine, Contraction("abcd", "aebf", "fdec", dict(a=72, b=72, c=72, d=72, e=72, f=72), F64), 1)
+    u = d["umma"]
+    assert d["kernel"] == "dmma_f64_tma" and (u["a_major"], u["b_major"], u["a_slab_w"], u["b_slab_w"]) == ("MN", "K", 8, 8)
+    assert u["tiles_m"] == 41 and u["tiles_n"] == 81 and u["BK"] == 16        # ceil(5184 / 128), 5184 / 64
+    # a contracted extent of 24: k chunks of 8 (64-byte rows for the K-major operand) instead of 2 x 16
+    d = describe(engine, Contraction("abcdef", "degc", "gfab", dict(a=24, b=16, c=16, d=24, e=16, f=16, g=24), F64), 1)
+    assert d["kernel"] == "dmma_f64_tma" and d["umma"]["BK"] == 8 and d["umma"]["k_iters"] == 3
+    # narrow N: 128 x 32 tiles
+    d = describe(engine, Contraction("abc", "dca", "bd", dict(a=312, b=24, c=296, d=312), F64), 1)
+    assert d["kernel"] == "dmma_f64_tma" and d["umma"]["BN"] == 32
+    # few tiles and a long contracted extent: split-K, two work units per SM for the FP64 kernel, one for tcgen05
+    for st, lo, hi in ((F64, 280, 320), (0, 140, 160)):
+        d = describe(engine, Contraction("ab", "acd", "dbc", dict(a=312, b=296, c=296, d=312), st), 1)
+        u = d["umma"]
+        assert u["k_splits"] > 1 and lo <= u["tiles_m"] * u["tiles_n"] * u["k_splits"] <= hi, u
+    monkeypatch.setenv("TCONT_SPLITK", "1")
+    assert describe(engine, Contraction("ab", "acd", "dbc", dict(a=312, b=296, c=296, d=312), F64), 1)["umma"]["k_splits"] == 1
+
+
 def test_every_reference_pattern_plans(engine):
     for fx in golden_fixtures():
         c = fixture_contraction(fx)
