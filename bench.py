@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 # workload -> (modeC, modeA, modeB, extents, scalar, seed, lo, hi, shard mode, roofline bound, cpu-sample mode, cpu-sample extent)
 WORKLOADS = {
     "cfg1": ("abcd", "aebf", "fdec", dict(a=24, b=24, c=24, d=24, e=16, f=16), 1, 0, -1.0, 1.0, "d", "tensor", "d", 24),
-    "cfg2": ("abc", "adc", "db", dict(a=256, c=256, b=1024, d=1024), 0, 1, -1.0, 1.0, "c", "tensor", "c", 32),
+    "cfg2": ("abc", "adc", "db", dict(a=256, c=256, b=1024, d=1024), 0, 1, -1.0, 1.0, "c", "tensor", "c", 64),
     "cfg3": ("abcijk", "aeij", "bcek", dict(a=48, b=48, c=48, e=48, i=24, j=24, k=24), 1, 2, -0.5, 0.5, "k", "tensor", "k", 1),
     "cfg4": ("abcde", "efba", "cfd", dict(a=48, b=48, c=48, d=48, e=48, f=8), 0, 3, -1.0, 1.0, "d", "hbm", "d", 24),
     "cfg5": ("abcd", "aebf", "cfde", dict(a=128, b=128, c=128, d=128, e=128, f=128), 0, 4, -1.0, 1.0, "d", "tensor", "d", 1),
