@@ -144,7 +144,7 @@ class ExecutionPlan:
         return float(_lib.tcontb_plan_flops(self._h))
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and _lib is not None:   # (module globals are gone at interpreter exit)
             _lib.tcontb_plan_destroy(self._h)
             self._h = None
 
@@ -182,7 +182,7 @@ class ExecutionRun:
         return s.value
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and _lib is not None:
             _lib.tcontb_run_destroy(self._h)
             self._h = None
 

@@ -234,7 +234,7 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 int kd2 = w.it0 / (p.k_digit_ext[0] * p.k_digit_ext[1]);
                 for (int it = 0; it < w.n_it; ++it) {
                     const uint32_t ps = first + stage;
-                    const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + ps), phase ^ 1u, abort_flag));
+                    const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + ps), phase ^ 1u, abort_flag, 200u));
                     if (ok) {
                         if (lane == 0) mbar_arrive_expect_tx(smem_u32(bar_full + ps), stage_bytes);
                         __syncwarp();
@@ -283,7 +283,7 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 const uint32_t tm = w.tm, tn = w.tn;
                 const uint32_t slot = (i & 1u) * 2u + ((i >> 1) & 1u);  // group, buffer
                 const uint32_t use = i >> 2;                            // how often this slot was filled before
-                if (!mbar_wait(smem_u32(tab_empty + slot), (use & 1u) ^ 1u, abort_flag)) break;
+                if (!mbar_wait(smem_u32(tab_empty + slot), (use & 1u) ^ 1u, abort_flag, 500u)) break;
                 const uint32_t tab = tabs + slot * kTabBytes;
 #pragma unroll
                 for (int e3 = 0; e3 < 3; ++e3) {
@@ -372,7 +372,7 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     }
                     // last step: one look at the next stage's barrier; if its data is there, fetch from it
                     if (it + 1 < w.n_it)
-                        next_first = __all_sync(0xffffffffu, mbar_try_wait(smem_u32(bar_full + first + next_stage), next_phase));
+                        next_first = __all_sync(0xffffffffu, mbar_test_wait(smem_u32(bar_full + first + next_stage), next_phase));
                     if (next_first) {
                         const uint32_t nb = smem_u32(smem) + (first + next_stage) * stage_bytes;
                         qa = frag_addr<AMN>(nb + a_thread, step_k(0, fk), fr, rows64, a8), qb = frag_addr<BMN>(nb + b_thread, step_k(0, fk), fr, rows64, b8);

@@ -47,6 +47,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return done != 0;
 }
 
+// One look at the barrier without waiting (try_wait may suspend the thread for a while).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
 // Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit passes, or
 // immediately when another thread of the CTA already gave up.
 __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr)
@@ -73,11 +87,14 @@ __device__ __forceinline__ long long ld_shared_s64(uint32_t addr)
 // Bounded wait.  The fast path is a bare try_wait; every 256 failed polls it looks at the CTA's
 // abort flag (shared-memory word at `abort_addr`) and at the clock.  Returns false, and raises the
 // flag, when the limit passes; returns false at once when another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_addr)
+// `sleep_ns` > 0: the thread sleeps that long after a failed poll, for warps whose polling would
+// otherwise take issue slots from the warps doing the arithmetic on the same scheduler.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_addr, uint32_t sleep_ns = 0)
 {
     unsigned long long t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (sleep_ns) __nanosleep(sleep_ns);
         if ((spin & 255u) == 255u || spin == 0) {
             if (ld_shared_u32(abort_addr)) return false;
             if (spin == 0) continue;
