@@ -175,7 +175,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--backend", default="model", choices=["model", "cogent", "ttgt"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--e2e-steps", type=lambda v: max(1, int(v)), default=5, help="passes through the host-buffer entry point (at least 1)")
     ap.add_argument("--extent", action="append", default=[], metavar="MODE=N",
                     help="override one extent of the workload (repeatable), e.g. --workload cfg3 --extent k=4 for a "
                          "case small enough to profile; the JSON line then names the changed extents")

@@ -413,10 +413,20 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                         if (run4 && (reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
                             st_global_cs_v4f64(dst, acc[2 * pr][j][0], acc[2 * pr + 1][j][0], acc[2 * pr][j][1], acc[2 * pr + 1][j][1]);
                         } else {
-                            if (cm0 >= 0) __stcs(C + cm0 + cn[j], acc[2 * pr][j][0]);
-                            if (cm1 >= 0) __stcs(C + cm1 + cn[j], acc[2 * pr + 1][j][0]);
-                            if (cm2 >= 0) __stcs(C + cm2 + cn[j], acc[2 * pr][j][1]);
-                            if (cm3 >= 0) __stcs(C + cm3 + cn[j], acc[2 * pr + 1][j][1]);
+                            // ragged or odd-aligned runs: 16 bytes where two rows are neighbours, else one by one
+                            if (cm0 >= 0 && cm1 == cm0 + 1 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                                __stcs(reinterpret_cast<double2*>(dst), make_double2(acc[2 * pr][j][0], acc[2 * pr + 1][j][0]));
+                            } else {
+                                if (cm0 >= 0) __stcs(dst, acc[2 * pr][j][0]);
+                                if (cm1 >= 0) __stcs(C + cm1 + cn[j], acc[2 * pr + 1][j][0]);
+                            }
+                            double* dst2 = C + cm2 + cn[j];
+                            if (cm2 >= 0 && cm3 == cm2 + 1 && (reinterpret_cast<uintptr_t>(dst2) & 15u) == 0) {
+                                __stcs(reinterpret_cast<double2*>(dst2), make_double2(acc[2 * pr][j][1], acc[2 * pr + 1][j][1]));
+                            } else {
+                                if (cm2 >= 0) __stcs(dst2, acc[2 * pr][j][1]);
+                                if (cm3 >= 0) __stcs(C + cm3 + cn[j], acc[2 * pr + 1][j][1]);
+                            }
                         }
                     }
                     acc[2 * pr][j][0] = acc[2 * pr][j][1] = acc[2 * pr + 1][j][0] = acc[2 * pr + 1][j][1] = 0.0;

@@ -111,6 +111,7 @@ FP64_SHAPES = {
     "case20_like": Contraction("abcd", "aebf", "dfce", dict(a=72, b=24, c=24, d=72, e=24, f=16), F64),   # both MN-major on extents of 72: slabs of 8
     "slab8_k8": Contraction("abcd", "aebf", "dfce", dict(a=40, b=60, c=40, d=24, e=24, f=3), F64),        # slabs of 8 with a k chunk of 8 (f = 3: mostly zero fill)
     "three_k": Contraction("ab", "axyz", "xyzb", dict(a=640, b=512, x=8, y=3, z=5), F64),               # three contracted modes (the reference stops at two)
+    "cfg3_a6": Contraction("abcijk", "aeij", "bcek", dict(a=6, b=24, c=24, e=48, i=12, j=12, k=12), F64),  # cfg3 cut by a over 8 GPUs: 48-byte runs
     "kmajor_k24": Contraction("ab", "ka", "kb", dict(a=1537, b=1409, k=24), F64),                      # k chunk of 8: 64-byte K-major rows
     "mixed_k40": Contraction("ab", "ak", "kb", dict(a=1200, b=1000, k=40), F64),                       # the same with an MN-major A
     "case33_like": Contraction("abcdef", "degc", "gfab", dict(a=24, b=16, c=16, d=24, e=16, f=16, g=24), F64),
