@@ -553,7 +553,9 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
         rate = c.dmma_f64_tflops * wave_efficiency(u.tiles_m * u.tiles_n * u.k_splits) / tma_padding;
         // Rows of a slab that are not contiguous in C are stored element by element
         // (abcdef-dega-gfbc: 37.7 M elements of C, 1.08 ms against 0.10 ms for its coalesced siblings).
-        if (u.a.row_elem_cstride != 1) scatter_us = double(p.sizeC) * double(u.k_splits) * c.scatter_store_ps * 1e-6;
+        // (runs shorter than 64 bytes count as scattered too: cfg3 cut to a = 6 ran at 17.6 TFLOP/s here
+        // against 20.2 on the gather kernel, which sees those rows as one flat index)
+        if (u.a.row_elem_cstride != 1 || u.a.slab_mode_ext < 8) scatter_us = double(p.sizeC) * double(u.k_splits) * c.scatter_store_ps * 1e-6;
     }
     if (kernel == KERNEL_DMMA_F64) {
         const int64_t bn = p.Ntot <= 48 ? 32 : 64, bm = p.Ntot <= 48 ? 256 : 128;
@@ -586,6 +588,7 @@ int pick_kernel(const Problem& p, const UmmaSpec& u, const CostTable& c)
     if (p.scalar_type != 1) return KERNEL_SIMT;
     const char* k = std::getenv("TCONT_KERNEL");
     if (k && std::strcmp(k, "simt") == 0) return KERNEL_SIMT;
+    if (k && std::strcmp(k, "tma") == 0 && u.eligible && u.elt == 8) return KERNEL_DMMA_F64_TMA;
     int best = KERNEL_SIMT;
     double best_us = contraction_us(p, KERNEL_SIMT, u, c);
     const int64_t bn = p.Ntot <= 48 ? 32 : 64, bm = p.Ntot <= 48 ? 256 : 128;  // the gather kernel's smallest fitting tile

@@ -138,6 +138,17 @@ def test_fp64_tensor_path(engine, oracle, monkeypatch, name, kernel):
     check(oracle, c, A, B, out, desc)
 
 
+@pytest.mark.parametrize("name", ["cfg3_a6", "scattered_store", "slab8_k8", "kmajor_k24"])
+def test_fp64_tma_kernel_forced(engine, oracle, monkeypatch, name):
+    """Shapes the cost table may send elsewhere (short or scattered row runs), held on the TMA-fed kernel."""
+    monkeypatch.setenv("TCONT_KERNEL", "tma")
+    c = FP64_SHAPES[name]
+    A, B = oracle.inputs(c, 33, -1.0, 1.0)
+    out, desc = run_contraction(engine, c, A, B, 1)
+    assert desc["kernel"] == "dmma_f64_tma"
+    check(oracle, c, A, B, out, desc)
+
+
 @pytest.mark.parametrize("name", ["gemm_mn_k", "kmajor_long", "case21_like", "long_k_ragged"])
 def test_fp64_split_k_forced(engine, oracle, monkeypatch, name):
     monkeypatch.setenv("TCONT_SPLITK", "3")
