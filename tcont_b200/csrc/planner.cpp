@@ -316,7 +316,7 @@ void merge_slabs(UmmaOperand* o, int BK, int cta_slabs)
     *o = n;
 }
 
-void plan_umma(const Problem& p, UmmaSpec* u)
+void plan_umma(const Problem& p, const CostTable& cost, UmmaSpec* u)
 {
     u->eligible = false;
     const bool f64 = p.scalar_type == 1;
@@ -469,16 +469,35 @@ void plan_umma(const Problem& p, UmmaSpec* u)
     u->stages = std::max(2, std::min(8, budget / stage_bytes));
     if (f64) u->stages &= ~1;  // one ring of stages per consumer group
     u->smem_bytes = u->stages * stage_bytes + 8 * 1024 + 1024;
-    // Split-K: with clearly less than one wave of tiles and a long contracted extent, cut the k
-    // iterations into ranges computed as separate work units (partials summed by a second kernel).
-    // The FP64 kernel wants two units per SM, one for each of its consumer groups.
+    // Split-K: with few waves of tiles and a long contracted extent, cut the k iterations into ranges
+    // computed as separate work units (partials summed by a second kernel).  Of the admissible counts
+    // (ranges of at least 4 iterations, workspace of at most 512 MB) the one with the smallest estimate
+    // wins: arithmetic over the share of the last wave's SMs that have a unit, plus the partials written
+    // and read back.  A wave is 148 units for the tcgen05 kernel and 296 for the FP64 kernel, which
+    // wants a unit for each of its two consumer groups.
     {
         const int64_t tiles = (u->pair ? ceil_div(u->tiles_m, 2) : u->tiles_m) * u->tiles_n;
-        const int64_t target = f64 ? 296 : 148;
+        const int64_t wave = f64 ? 296 : 148;
+        const double flops = 2.0 * double(u->tiles_m * u->BM) * double(u->tiles_n * u->BN) * double(u->k_iters * u->BK);
+        const double rate = (f64 ? cost.dmma_f64_tflops : cost.umma_tf32_tflops) * 1e6;  // flops per microsecond
+        auto estimate = [&](int64_t s) {
+            const int64_t units = tiles * s;
+            const double eff = double(units) / double(ceil_div(units, wave) * wave);
+            return flops / (rate * eff) + (s > 1 ? cost.launch_us + 2.0 * double(s) * double(p.sizeC) * elt / (cost.hbm_gbs * 1e3) : 0.0);
+        };
         int64_t splits = 1;
-        if (tiles * 4 < target * 3 && u->k_iters >= 8) splits = std::min<int64_t>(ceil_div(target, tiles), u->k_iters / 4);
-        if (const char* e = std::getenv("TCONT_SPLITK")) splits = std::max<int64_t>(1, std::min<int64_t>(std::atoll(e), u->k_iters));
-        while (splits > 1 && double(splits) * double(p.sizeC) * elt > 512.0 * 1024 * 1024) --splits;  // workspace
+        if (tiles < 4 * wave && u->k_iters >= 8) {
+            double best = estimate(1);
+            for (int64_t s = 2; s <= std::min<int64_t>(64, u->k_iters / 4); ++s) {
+                if (double(s) * double(p.sizeC) * elt > 512.0 * 1024 * 1024) break;  // workspace
+                const double e = estimate(s);
+                if (e < 0.97 * best) best = e, splits = s;  // (a split has to pay for its second kernel)
+            }
+        }
+        if (const char* e = std::getenv("TCONT_SPLITK")) {
+            splits = std::max<int64_t>(1, std::min<int64_t>(std::atoll(e), u->k_iters));
+            while (splits > 1 && double(splits) * double(p.sizeC) * elt > 512.0 * 1024 * 1024) --splits;
+        }
         u->k_iters_per_split = ceil_div(u->k_iters, splits);
         u->k_splits = static_cast<int>(ceil_div(u->k_iters, u->k_iters_per_split));
     }
@@ -687,7 +706,7 @@ int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* 
     pl.flops = 2.0 * std::sqrt(double(pl.sizeL) * double(pl.sizeR) * double(pl.sizeC));
 
     UmmaSpec direct_umma;
-    plan_umma(direct, &direct_umma);
+    plan_umma(direct, cost, &direct_umma);
     const int direct_kernel = pick_kernel(direct, direct_umma, cost);
     pl.est_direct_us = contraction_us(direct, direct_kernel, direct_umma, cost);
 
@@ -754,7 +773,7 @@ int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* 
     rc = build_problem(pl.modeC, roleA_dst, roleB_dst, pl.ext_mode, pl.ext_val, scalar_type, &ttgt, err);
     if (rc) return rc;
     UmmaSpec ttgt_umma;
-    plan_umma(ttgt, &ttgt_umma);
+    plan_umma(ttgt, cost, &ttgt_umma);
     const int ttgt_kernel = pick_kernel(ttgt, ttgt_umma, cost);
     TransposeSpec tA, tB;
     fill_transpose(roleA_src, roleA_dst, pl.ext_mode, pl.ext_val, &tA);

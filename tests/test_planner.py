@@ -99,11 +99,16 @@ def test_fp64_row_widths_and_split_k(engine, monkeypatch):
     # narrow N: 128 x 32 tiles
     d = describe(engine, Contraction("abc", "dca", "bd", dict(a=312, b=24, c=296, d=312), F64), 1)
     assert d["kernel"] == "dmma_f64_tma" and d["umma"]["BN"] == 32
-    # few tiles and a long contracted extent: split-K, two work units per SM for the FP64 kernel, one for tcgen05
-    for st, lo, hi in ((F64, 280, 320), (0, 140, 160)):
+    # few tiles and a long contracted extent: split-K into a count of work units that fills whole waves
+    # (296 units per wave for the FP64 kernel with its two consumer groups, 148 for tcgen05)
+    for st, wave in ((F64, 296), (0, 148)):
         d = describe(engine, Contraction("ab", "acd", "dbc", dict(a=312, b=296, c=296, d=312), st), 1)
         u = d["umma"]
-        assert u["k_splits"] > 1 and lo <= u["tiles_m"] * u["tiles_n"] * u["k_splits"] <= hi, u
+        units = u["tiles_m"] * u["tiles_n"] * u["k_splits"]
+        assert u["k_splits"] > 1 and units / (-(-units // wave) * wave) >= 0.9, u
+    # a little over one wave of tiles (162 on 148 SMs) is cut as well
+    d = describe(engine, Contraction("abc", "adec", "ebd", dict(a=72, b=72, c=72, d=72, e=72), 0), 1)
+    assert d["umma"]["tiles_m"] * d["umma"]["tiles_n"] == 162 and d["umma"]["k_splits"] >= 3
     monkeypatch.setenv("TCONT_SPLITK", "1")
     assert describe(engine, Contraction("ab", "acd", "dbc", dict(a=312, b=296, c=296, d=312), F64), 1)["umma"]["k_splits"] == 1
 
