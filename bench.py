@@ -114,6 +114,9 @@ def cpu_baseline(name: str, max_seconds: float = 60.0):
     ext[smode] = min(sext, full)
     c = Contraction(mC, mA, mB, ext, st)
     oracle = Oracle()
+    # all the cores this process may run on, whatever OMP_NUM_THREADS the launcher exported
+    # (torch.distributed.run sets it to 1 for several ranks)
+    oracle.set_num_threads(len(os.sched_getaffinity(0)))
     A, B = oracle.inputs(c, seed, lo, hi)
     sample = f"{name} with {smode}={ext[smode]} of {full} (a {ext[smode]}/{full} slab of the outputs, all other modes full)"
     use_ref = RefVerifier.available() and name in REF_CASE

@@ -328,3 +328,15 @@ int oracle_num_threads(void)
     return 1;
 #endif
 }
+
+/* Sets the OpenMP team size of later calls made from the calling thread.  A launcher may have
+ * exported OMP_NUM_THREADS=1 (torch.distributed.run does for several ranks); the timed CPU baseline
+ * asks for all the cores the process may run on instead. */
+void oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

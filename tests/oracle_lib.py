@@ -89,6 +89,12 @@ class Oracle:
     def num_threads(self) -> int:
         return int(self.lib.oracle_num_threads())
 
+    def set_num_threads(self, n: int):
+        """Team size of later OpenMP regions entered from this thread (the reference verifier shares the
+        same OpenMP runtime, so this also governs RefVerifier.verify)."""
+        self.lib.oracle_set_num_threads.argtypes = [C.c_int]
+        self.lib.oracle_set_num_threads(int(n))
+
     def fill(self, n: int, scalar_type: int, seed: int, offset: int, lo: float, hi: float) -> np.ndarray:
         out = np.empty(n, dtype=np.float64 if scalar_type == F64 else np.float32)
         self.lib.oracle_fill_uniform(_ptr(out), scalar_type, n, seed, offset, lo, hi)
