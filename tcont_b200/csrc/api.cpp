@@ -92,7 +92,14 @@ struct tcontb_run {
     UmmaParams umma{};
     CUtensorMap tmA{}, tmB{};
     DeviceBuffer status;
-    DeviceBuffer splitk;  // partial tensors of a split-K contraction, k_splits copies of C
+    DeviceBuffer splitk;  // partial tensors of a split-K contraction, k_splits copies of C (three times that with tf32x3)
+    // Error-compensated Float32 (TCONT_TF32X3=1, tcgen05 kernel only): the part of each operand that
+    // narrowing to TF32 drops, its tensor maps, and where the kernel's operands lie.
+    bool tf32x3 = false;
+    DeviceBuffer loA, loB;
+    CUtensorMap tmAlo{}, tmBlo{};
+    const void *kernA = nullptr, *kernB = nullptr;
+    int64_t kernA_elements = 0, kernB_elements = 0;
     DeviceBuffer prof;  // cycle counters of the tcgen05 kernel, only with TCONT_UMMA_PROF=1
     // stage timing
     bool stage_timing = false;
@@ -259,10 +266,25 @@ tcontb_status finish_run(tcontb_run* run)
         run->umma.k_iters_per_split = static_cast<int>(u.k_iters_per_split);
         run->umma.split_stride = pl.sizeC;
         void* out = run->dC;
-        if (u.k_splits > 1) {
-            TC_CUDA(run->splitk.alloc(static_cast<size_t>(u.k_splits) * static_cast<size_t>(pl.sizeC) * run->elt));
+        const char* x3 = std::getenv("TCONT_TF32X3");
+        run->tf32x3 = pl.kernel == KERNEL_UMMA_TF32 && x3 && x3[0] == '1';
+        if (u.k_splits > 1 || run->tf32x3) {
+            TC_CUDA(run->splitk.alloc(static_cast<size_t>(run->tf32x3 ? 3 : 1) * static_cast<size_t>(u.k_splits) *
+                                      static_cast<size_t>(pl.sizeC) * run->elt));
             out = run->splitk.ptr;
             run->kernels_per_launch++;
+        }
+        if (run->tf32x3) {
+            // C = hi(A) hi(B) + hi(A) lo(B) + lo(A) hi(B): the tensor core takes hi() itself (it truncates),
+            // lo() is computed per launch into these buffers, and the three products are partials of the
+            // split-K sum.  Accuracy is that of fp32 accumulation; the cost is three contractions.
+            run->kernA = kA;
+            run->kernB = kB;
+            run->kernA_elements = pl.tA.needed ? pl.tA.elements : (p.swapped ? pl.sizeR : pl.sizeL);
+            run->kernB_elements = pl.tB.needed ? pl.tB.elements : (p.swapped ? pl.sizeL : pl.sizeR);
+            TC_CUDA(run->loA.alloc(static_cast<size_t>(run->kernA_elements) * run->elt));
+            TC_CUDA(run->loB.alloc(static_cast<size_t>(run->kernB_elements) * run->elt));
+            run->kernels_per_launch += 4;  // two residual passes, two more contractions
         }
         run->umma.C = static_cast<float*>(out);
         run->umma.C64 = static_cast<double*>(out);
@@ -279,6 +301,12 @@ tcontb_status finish_run(tcontb_run* run)
         if (st != TCONTB_OK) return st;
         st = encode_map(u.b, kB, u.elt, &run->tmB);
         if (st != TCONTB_OK) return st;
+        if (run->tf32x3) {
+            st = encode_map(u.a, run->loA.ptr, u.elt, &run->tmAlo);
+            if (st != TCONTB_OK) return st;
+            st = encode_map(u.b, run->loB.ptr, u.elt, &run->tmBlo);
+            if (st != TCONTB_OK) return st;
+        }
         if (pl.kernel == KERNEL_UMMA_TF32) TC_CUDA(umma_tf32_configure(u.smem_bytes));
         else TC_CUDA(dmma_tma_configure(u.smem_bytes));
     } else {
@@ -710,7 +738,16 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
     if (t) TC_CUDA(cudaEventRecord(run->ev[1], run->stream));
     if (pl.tB.needed) TC_CUDA(launch_transpose(run->roleB_src(), run->tbufB.ptr, run->tpB, static_cast<int>(run->elt), run->stream));
     if (t) TC_CUDA(cudaEventRecord(run->ev[2], run->stream));
-    if (pl.kernel == KERNEL_UMMA_TF32)
+    if (pl.kernel == KERNEL_UMMA_TF32 && run->tf32x3) {
+        TC_CUDA(launch_tf32_residual(static_cast<const float*>(run->kernA), static_cast<float*>(run->loA.ptr), run->kernA_elements, run->stream));
+        TC_CUDA(launch_tf32_residual(static_cast<const float*>(run->kernB), static_cast<float*>(run->loB.ptr), run->kernB_elements, run->stream));
+        const CUtensorMap* maps[3][2] = {{&run->tmA, &run->tmB}, {&run->tmA, &run->tmBlo}, {&run->tmAlo, &run->tmB}};
+        for (int pass = 0; pass < 3; ++pass) {
+            UmmaParams q = run->umma;
+            q.C = static_cast<float*>(run->splitk.ptr) + static_cast<long long>(pass) * pl.umma.k_splits * pl.sizeC;
+            TC_CUDA(launch_umma_tf32(q, maps[pass][0], maps[pass][1], pl.umma.smem_bytes, run->num_sms, run->stream));
+        }
+    } else if (pl.kernel == KERNEL_UMMA_TF32)
         TC_CUDA(launch_umma_tf32(run->umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
     else if (pl.kernel == KERNEL_DMMA_F64_TMA)
         TC_CUDA(launch_dmma_tma(run->umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
@@ -719,7 +756,8 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
     else
         TC_CUDA(launch_simt_contract(run->simt, pl.scalar_type, run->stream));
     if (run->splitk.ptr)
-        TC_CUDA(launch_splitk_reduce(run->splitk.ptr, run->dC, pl.sizeC, pl.umma.k_splits, pl.sizeC, static_cast<int>(run->elt), run->stream));
+        TC_CUDA(launch_splitk_reduce(run->splitk.ptr, run->dC, pl.sizeC, pl.umma.k_splits * (run->tf32x3 ? 3 : 1), pl.sizeC,
+                                     static_cast<int>(run->elt), run->stream));
     if (t) {
         TC_CUDA(cudaEventRecord(run->ev[3], run->stream));
         run->ev_valid = true;

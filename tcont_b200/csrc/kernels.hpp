@@ -85,4 +85,7 @@ cudaError_t dmma_tma_configure(int smem_bytes);
 cudaError_t launch_splitk_reduce(const void* partial, void* C, long long elements, int splits, long long stride, int elt_bytes,
                                  cudaStream_t stream);
 
+// ---- error-compensated Float32 (splitk_reduce.cu): lo = x - truncate_to_tf32(x), exact in fp32 ----
+cudaError_t launch_tf32_residual(const float* x, float* lo, long long elements, cudaStream_t stream);
+
 }  // namespace tcontb
