@@ -98,6 +98,14 @@ tcontb_status tcontb_run_set_stream(tcontb_run* run, void* cuda_stream);
 /* Replaces the run's inputs by an asynchronous host-to-device copy on the run's stream. */
 tcontb_status tcontb_run_upload_inputs(tcontb_run* run, const void* a_host, const void* b_host);
 
+/* Beyond the reference, whose backends always overwrite (alpha = 1, beta = 0: cublasGemmEx scalars at
+ * backends/ttgt_cutt/src/ttgt_cutt.cpp:742-743, generated kernels store a zeroed accumulator): later
+ * launches compute C = alpha * (A*B) + beta * C.  With other values than (1, 0) the contraction
+ * writes a workspace of the size of C (allocated by this call, not by the launches) and the
+ * partial-sum pass applies the scalars; C is read only when beta is not zero.  Not available on a
+ * run that spans several GPUs. */
+tcontb_status tcontb_run_set_scalars(tcontb_run* run, double alpha, double beta);
+
 /* TconT::launch (src/tcont.cpp:102-108): one contraction, asynchronous. */
 tcontb_status tcontb_run_launch(tcontb_run* run);
 /* TconT::warmup (src/tcont.cpp:110-124): `iterations` launches, then a device synchronize. */

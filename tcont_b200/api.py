@@ -72,6 +72,7 @@ _lib.tcontb_run_create_on_device.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p,
 _lib.tcontb_run_destroy.argtypes = [C.c_void_p]
 _lib.tcontb_run_set_stream.argtypes = [C.c_void_p, C.c_void_p]
 _lib.tcontb_run_upload_inputs.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+_lib.tcontb_run_set_scalars.argtypes = [C.c_void_p, C.c_double, C.c_double]
 _lib.tcontb_run_launch.argtypes = [C.c_void_p]
 _lib.tcontb_run_warmup.argtypes = [C.c_void_p, C.c_int]
 _lib.tcontb_run_zero_output.argtypes = [C.c_void_p]
@@ -159,6 +160,10 @@ class ExecutionRun:
 
     def set_stream(self, cuda_stream: int):
         _check(_lib.tcontb_run_set_stream(self._h, C.c_void_p(cuda_stream)))
+
+    def set_scalars(self, alpha: float = 1.0, beta: float = 0.0):
+        """Later launches compute C = alpha * (A*B) + beta * C; (1, 0) is the reference's overwrite."""
+        _check(_lib.tcontb_run_set_scalars(self._h, float(alpha), float(beta)))
 
     def time_launches(self, iterations: int):
         ms, n = C.c_float(), C.c_int64()

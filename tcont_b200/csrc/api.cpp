@@ -4,6 +4,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <cmath>
 #include <cstring>
 #include <ctime>
 #include <memory>
@@ -101,6 +102,10 @@ struct tcontb_run {
     const void *kernA = nullptr, *kernB = nullptr;
     int64_t kernA_elements = 0, kernB_elements = 0;
     DeviceBuffer prof;  // cycle counters of the tcgen05 kernel, only with TCONT_UMMA_PROF=1
+    // C = alpha * (A*B) + beta * C (tcontb_run_set_scalars); the reference's semantics are alpha 1, beta 0.
+    // With other values the contraction writes a workspace and the partial-sum pass applies the scalars.
+    double alpha = 1.0, beta = 0.0;
+    DeviceBuffer scaled_ws;
     // stage timing
     bool stage_timing = false;
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -712,6 +717,28 @@ tcontb_status tcontb_run_upload_inputs(tcontb_run* run, const void* a_host, cons
     return TCONTB_OK;
 }
 
+tcontb_status tcontb_run_set_scalars(tcontb_run* run, double alpha, double beta)
+{
+    if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    if (!std::isfinite(alpha) || !std::isfinite(beta)) return fail(TCONTB_INVALID_ARGUMENT, "alpha and beta must be finite");
+    TC_NOT_SHARDED(run, "alpha and beta");
+    const bool scaled = alpha != 1.0 || beta != 0.0;
+    if (scaled && !run->splitk.ptr && !run->scaled_ws.ptr) {
+        // allocated here, once, so that launches stay free of allocations
+        TC_CUDA(run->scaled_ws.alloc(static_cast<size_t>(run->plan.sizeC) * run->elt));
+    }
+    const bool was = run->alpha != 1.0 || run->beta != 0.0;
+    if (!run->splitk.ptr) run->kernels_per_launch += (scaled ? 1 : 0) - (was ? 1 : 0);
+    run->alpha = alpha;
+    run->beta = beta;
+    // the parts of a pipelined host-buffer pass work on ranges of this run's C
+    for (auto& part : run->pipe.parts) {
+        const tcontb_status st = tcontb_run_set_scalars(part.get(), alpha, beta);
+        if (st != TCONTB_OK) return st;
+    }
+    return TCONTB_OK;
+}
+
 tcontb_status tcontb_run_launch(tcontb_run* run)
 {
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
@@ -733,6 +760,16 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
     }
     const Plan& pl = run->plan;
     const bool t = run->stage_timing;
+    // Other scalars than (1, 0): the kernel writes the workspace instead of C (a split-K run does anyway)
+    const bool scaled = run->alpha != 1.0 || run->beta != 0.0;
+    const bool redirect = scaled && !run->splitk.ptr;
+    UmmaParams umma = run->umma;
+    SimtParams simt = run->simt;
+    if (redirect) {
+        umma.C = static_cast<float*>(run->scaled_ws.ptr);
+        umma.C64 = static_cast<double*>(run->scaled_ws.ptr);
+        simt.C = run->scaled_ws.ptr;
+    }
     if (t) TC_CUDA(cudaEventRecord(run->ev[0], run->stream));
     if (pl.tA.needed) TC_CUDA(launch_transpose(run->roleA_src(), run->tbufA.ptr, run->tpA, static_cast<int>(run->elt), run->stream));
     if (t) TC_CUDA(cudaEventRecord(run->ev[1], run->stream));
@@ -743,21 +780,24 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
         TC_CUDA(launch_tf32_residual(static_cast<const float*>(run->kernB), static_cast<float*>(run->loB.ptr), run->kernB_elements, run->stream));
         const CUtensorMap* maps[3][2] = {{&run->tmA, &run->tmB}, {&run->tmA, &run->tmBlo}, {&run->tmAlo, &run->tmB}};
         for (int pass = 0; pass < 3; ++pass) {
-            UmmaParams q = run->umma;
+            UmmaParams q = umma;
             q.C = static_cast<float*>(run->splitk.ptr) + static_cast<long long>(pass) * pl.umma.k_splits * pl.sizeC;
             TC_CUDA(launch_umma_tf32(q, maps[pass][0], maps[pass][1], pl.umma.smem_bytes, run->num_sms, run->stream));
         }
     } else if (pl.kernel == KERNEL_UMMA_TF32)
-        TC_CUDA(launch_umma_tf32(run->umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
+        TC_CUDA(launch_umma_tf32(umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
     else if (pl.kernel == KERNEL_DMMA_F64_TMA)
-        TC_CUDA(launch_dmma_tma(run->umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
+        TC_CUDA(launch_dmma_tma(umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
     else if (pl.kernel == KERNEL_DMMA_F64)
-        TC_CUDA(launch_dmma_contract(run->simt, run->num_sms, run->stream));
+        TC_CUDA(launch_dmma_contract(simt, run->num_sms, run->stream));
     else
-        TC_CUDA(launch_simt_contract(run->simt, pl.scalar_type, run->stream));
+        TC_CUDA(launch_simt_contract(simt, pl.scalar_type, run->stream));
     if (run->splitk.ptr)
         TC_CUDA(launch_splitk_reduce(run->splitk.ptr, run->dC, pl.sizeC, pl.umma.k_splits * (run->tf32x3 ? 3 : 1), pl.sizeC,
-                                     static_cast<int>(run->elt), run->stream));
+                                     static_cast<int>(run->elt), run->stream, run->alpha, run->beta));
+    else if (redirect)
+        TC_CUDA(launch_splitk_reduce(run->scaled_ws.ptr, run->dC, pl.sizeC, 1, pl.sizeC, static_cast<int>(run->elt), run->stream,
+                                     run->alpha, run->beta));
     if (t) {
         TC_CUDA(cudaEventRecord(run->ev[3], run->stream));
         run->ev_valid = true;
@@ -902,6 +942,10 @@ tcontb_status tcontb_run_contract_host(tcontb_run* run, const void* a_host, cons
         TC_CUDA(cudaStreamWaitEvent(run->stream, pp.ev_other, 0));
         for (size_t i = 0; i < n; ++i) {
             TC_CUDA(cudaStreamWaitEvent(run->stream, pp.ev_in[i], 0));
+            if (pp.parts[i]->alpha != run->alpha || pp.parts[i]->beta != run->beta) {
+                const tcontb_status ss = tcontb_run_set_scalars(pp.parts[i].get(), run->alpha, run->beta);
+                if (ss != TCONTB_OK) return ss;
+            }
             const tcontb_status ls = tcontb_run_launch(pp.parts[i].get());
             if (ls != TCONTB_OK) return ls;
             TC_CUDA(cudaEventRecord(pp.ev_done[i], run->stream));

@@ -82,8 +82,9 @@ cudaError_t launch_dmma_tma(const UmmaParams& p, const void* tmapA, const void* 
 cudaError_t dmma_tma_configure(int smem_bytes);
 
 // ---- split-K: C[e] = sum over s of partial[s * stride + e], s ascending (splitk_reduce.cu) ----
+// With alpha != 1 or beta != 0: C[e] = alpha * sum + beta * C[e] (C is read only when beta != 0).
 cudaError_t launch_splitk_reduce(const void* partial, void* C, long long elements, int splits, long long stride, int elt_bytes,
-                                 cudaStream_t stream);
+                                 cudaStream_t stream, double alpha = 1.0, double beta = 0.0);
 
 // ---- error-compensated Float32 (splitk_reduce.cu): lo = x - truncate_to_tf32(x), exact in fp32 ----
 cudaError_t launch_tf32_residual(const float* x, float* lo, long long elements, cudaStream_t stream);

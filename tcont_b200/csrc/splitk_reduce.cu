@@ -19,7 +19,8 @@ namespace {
 
 template <typename T, typename V, int W>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const T* __restrict__ partial, T* __restrict__ C, long long elements,
-                                                           int splits, long long stride, bool vector_ok)
+                                                           int splits, long long stride, bool vector_ok, bool scaled, T alpha,
+                                                           T beta)
 {
     const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
     long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -36,6 +37,16 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const T* __restrict_
                     acc.w += v.w;
                 }
             }
+            if (scaled) {  // C = alpha * sum + beta * C; C is read only when beta is not zero
+                V old{};
+                if (beta != T(0)) old = reinterpret_cast<const V*>(C)[i];
+                acc.x = alpha * acc.x + beta * old.x;
+                acc.y = alpha * acc.y + beta * old.y;
+                if constexpr (W == 4) {
+                    acc.z = alpha * acc.z + beta * old.z;
+                    acc.w = alpha * acc.w + beta * old.w;
+                }
+            }
             __stcs(reinterpret_cast<V*>(C) + i, acc);
         }
         i = nv * W + (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x);
@@ -43,6 +54,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const T* __restrict_
     for (; i < elements; i += step) {
         T acc = partial[i];
         for (int s = 1; s < splits; ++s) acc += partial[static_cast<long long>(s) * stride + i];
+        if (scaled) acc = alpha * acc + (beta != T(0) ? beta * C[i] : T(0));
         C[i] = acc;
     }
 }
@@ -83,8 +95,9 @@ cudaError_t launch_tf32_residual(const float* x, float* lo, long long elements, 
 }
 
 cudaError_t launch_splitk_reduce(const void* partial, void* C, long long elements, int splits, long long stride, int elt_bytes,
-                                 cudaStream_t stream)
+                                 cudaStream_t stream, double alpha, double beta)
 {
+    const bool scaled = alpha != 1.0 || beta != 0.0;
     if (elements <= 0 || splits < 1) return cudaErrorInvalidValue;
     const int w = elt_bytes == 8 ? 2 : 4;
     const bool vector_ok = reinterpret_cast<uintptr_t>(partial) % 16 == 0 && reinterpret_cast<uintptr_t>(C) % 16 == 0 &&
@@ -93,10 +106,11 @@ cudaError_t launch_splitk_reduce(const void* partial, void* C, long long element
     const unsigned grid = static_cast<unsigned>(std::min<long long>((work + 255) / 256, 148ll * 8));
     if (elt_bytes == 8)
         splitk_reduce_kernel<double, double2, 2><<<grid, 256, 0, stream>>>(static_cast<const double*>(partial), static_cast<double*>(C),
-                                                                            elements, splits, stride, vector_ok);
+                                                                            elements, splits, stride, vector_ok, scaled, alpha, beta);
     else
         splitk_reduce_kernel<float, float4, 4><<<grid, 256, 0, stream>>>(static_cast<const float*>(partial), static_cast<float*>(C),
-                                                                          elements, splits, stride, vector_ok);
+                                                                          elements, splits, stride, vector_ok, scaled,
+                                                                          static_cast<float>(alpha), static_cast<float>(beta));
     return cudaGetLastError();
 }
 
