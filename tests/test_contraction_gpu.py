@@ -271,6 +271,64 @@ def test_cfg2_full_size_sampled_tf32x3(engine, oracle, monkeypatch):
     assert diff == 0 and nonfinite == 0
 
 
+SCALAR_CASES = {
+    # one per kernel family: name -> (descriptor, backend selection)
+    "tf32_tensor": (UMMA_SHAPES["cfg2_like"], 0),
+    "tf32_tensor_splitk": (UMMA_SHAPES["long_k"], 0),
+    "tf32_ttgt": (UMMA_SHAPES["cfg4_like"], 0),
+    "fp64_tma": (FP64_SHAPES["cfg3_like"], 1),
+    "fp64_cuda_cores": (Contraction("abc", "adc", "db", dict(a=13, c=5, b=11, d=7), F64), 0),
+}
+
+
+@pytest.mark.parametrize("name", list(SCALAR_CASES))
+def test_alpha_beta(engine, oracle, name):
+    """tcontb_run_set_scalars: C = alpha * (A*B) + beta * C.  (1, 0) is the reference's overwrite and gives the
+    same bits as a run that never set scalars; other values are held against overwrite results combined on the host."""
+    c, sel = SCALAR_CASES[name]
+    A, B = oracle.inputs(c, 13, -1.0, 1.0)
+    p = engine.plan(to_equation(engine, c, sel))
+    r = engine.prepare(p, A, B)
+    engine.launch(r)
+    base = engine.copy_output_to_host(r)            # C0 = A*B
+    r.set_scalars(1.0, 0.0)
+    engine.launch(r)
+    np.testing.assert_array_equal(engine.copy_output_to_host(r), base)
+    r.set_scalars(-0.5, 0.0)                        # pure scaling by a power of two: exact
+    engine.launch(r)
+    np.testing.assert_array_equal(engine.copy_output_to_host(r), base * base.dtype.type(-0.5))
+    r.set_scalars(2.0, 1.0)                         # accumulate on top of -0.5 * C0: 1.5 * C0, exact as well
+    engine.launch(r)
+    np.testing.assert_array_equal(engine.copy_output_to_host(r), base * base.dtype.type(1.5))
+    r.set_scalars(0.3, -0.7)                        # general scalars, rounding of one multiply-add per element
+    engine.launch(r)
+    want = 0.3 * base.astype(np.float64) - 0.7 * (1.5 * base.astype(np.float64))
+    tol = 1e-6 if c.scalar_type == F32 else 1e-14
+    np.testing.assert_allclose(engine.copy_output_to_host(r), want, rtol=tol, atol=tol * float(np.abs(base).max()))
+    r.set_scalars(1.0, 0.0)                         # back to overwrite
+    engine.launch(r)
+    np.testing.assert_array_equal(engine.copy_output_to_host(r), base)
+    assert r.device_status() == 0
+
+
+def test_alpha_beta_ignores_stale_output_when_beta_is_zero(engine, oracle):
+    """beta = 0 must not read C: a C full of NaN is overwritten, like BLAS."""
+    import torch
+    from tcont_b200 import api
+    c = Contraction("ab", "ak", "kb", dict(a=96, b=40, k=24), F64)
+    A, B = oracle.inputs(c, 3, -1.0, 1.0)
+    base, _ = run_contraction(engine, c, A, B, 1)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.full((c.size(c.modeC),), float("nan"), dtype=torch.float64, device="cuda")
+    r = api.prepare_on_device(engine.plan(to_equation(engine, c, 1)), dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), keep=(dA, dB, dC))
+    r.set_scalars(2.0, 0.0)
+    engine.launch(r)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(dC.cpu().numpy(), base * 2.0)
+    with pytest.raises(ValueError):
+        r.set_scalars(float("inf"), 0.0)
+
+
 @pytest.mark.skipif(os.environ.get("TCONT_TEST_CFG3", "1") != "1", reason="disabled by TCONT_TEST_CFG3")
 def test_cfg3_full_size_sampled(engine, oracle):
     _sampled_check(engine, oracle, "cfg3", 1_000_000)
