@@ -29,3 +29,24 @@ CONFIGS = {
 def to_equation(engine, c: Contraction, selection=0):
     return engine.TCEquation(c.modeC, c.modeA, c.modeB, dict(c.extent), "-", engine.ScalarType(c.scalar_type),
                              engine.BackendSelection(selection))
+
+
+def random_contraction(rng, scalar_type, max_out=200_000, max_macs=30_000_000) -> Contraction:
+    """A random well-formed contraction: 1-3 modes per group, ragged extents, random memory orders."""
+    pool = [1, 2, 3, 4, 5, 7, 8, 12, 16, 24, 32, 33, 40, 64, 72, 96, 128]
+    letters = list("abcdefghi")
+    while True:
+        nM, nN, nK = (int(rng.integers(1, 4)) for _ in range(3))
+        names = letters[: nM + nN + nK]
+        ext = {n: int(rng.choice(pool)) for n in names}
+        M, N, K = names[:nM], names[nM:nM + nN], names[nM + nN:]
+        out = 1
+        for n in M + N:
+            out *= ext[n]
+        macs = out
+        for n in K:
+            macs *= ext[n]
+        if out <= max_out and macs <= max_macs:
+            break
+    order = lambda modes: "".join(rng.permutation(modes))  # noqa: E731
+    return Contraction(order(M + N), order(M + K), order(N + K), ext, scalar_type)

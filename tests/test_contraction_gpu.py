@@ -11,7 +11,7 @@ import os
 import numpy as np
 import pytest
 
-from cases import CONFIGS, fixture_contraction, golden_fixtures, to_equation
+from cases import CONFIGS, fixture_contraction, golden_fixtures, random_contraction, to_equation
 from oracle_lib import F32, F64, Contraction
 
 pytestmark = pytest.mark.gpu
@@ -327,6 +327,22 @@ def test_alpha_beta_ignores_stale_output_when_beta_is_zero(engine, oracle):
     np.testing.assert_array_equal(dC.cpu().numpy(), base * 2.0)
     with pytest.raises(ValueError):
         r.set_scalars(float("inf"), 0.0)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_descriptors(engine, oracle, seed):
+    """Ten random descriptors per seed (1-3 modes per group, ragged extents, random memory orders, both precisions,
+    every backend selection) against the oracle, whatever kernel and route the planner picks for them."""
+    rng = np.random.default_rng(1000 + seed)
+    for i in range(10):
+        c = random_contraction(rng, (seed + i) % 2)
+        sel = int(rng.integers(0, 3))
+        A, B = oracle.inputs(c, 100 * seed + i, -1.0, 1.0)
+        out, desc = run_contraction(engine, c, A, B, sel)
+        try:
+            check(oracle, c, A, B, out, desc)
+        except AssertionError as e:
+            raise AssertionError(f"{c} selection {sel} -> {desc['backend']}/{desc['kernel']}: {e}") from e
 
 
 @pytest.mark.skipif(os.environ.get("TCONT_TEST_CFG3", "1") != "1", reason="disabled by TCONT_TEST_CFG3")

@@ -149,3 +149,26 @@ def test_flop_count_is_the_reference_formula(engine):
     assert p.flops == pytest.approx(2.0 * 65536 * 1024 * 1024)
     assert engine.compute_gflops(p.equation, 1.0) == pytest.approx(p.flops / 1e6)
     assert engine.compute_gflops(p.equation, 0.0) == 0.0
+
+
+def test_random_descriptors_plan_consistently(engine):
+    """300 random descriptors (1-3 modes per group, ragged extents, random orders, both precisions, every backend
+    selection): the planner accepts each one and its GEMM view multiplies out to the descriptor's extents."""
+    import numpy as np
+
+    from cases import random_contraction
+    rng = np.random.default_rng(2024)
+    for i in range(300):
+        c = random_contraction(rng, int(rng.integers(0, 2)))
+        sel = int(rng.integers(0, 3))
+        d = engine.plan(to_equation(engine, c, sel)).describe()
+        assert d["Mtot"] * d["Ntot"] == c.size(c.modeC), (i, c)
+        assert d["Mtot"] * d["Ktot"] in (c.size(c.modeA), c.size(c.modeB)), (i, c)
+        assert d["backend"] in ("direct", "ttgt") and d["kernel"] in ("simt", "umma_tf32", "dmma_f64", "dmma_f64_tma")
+        if sel == 1:
+            assert d["backend"] == "direct" and d["transpose_a"] is None and d["transpose_b"] is None
+        u = d["umma"]
+        if d["kernel"] in ("umma_tf32", "dmma_f64_tma"):
+            assert u["eligible"] and u["smem_bytes"] <= 227 * 1024
+            assert u["tiles_m"] * u["BM"] >= d["Mtot"] and u["tiles_n"] * u["BN"] >= d["Ntot"]
+            assert u["k_iters"] * u["BK"] >= d["Ktot"] and 1 <= u["k_splits"] <= u["k_iters"]
