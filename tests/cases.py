@@ -31,9 +31,12 @@ def to_equation(engine, c: Contraction, selection=0):
                              engine.BackendSelection(selection))
 
 
-def random_contraction(rng, scalar_type, max_out=200_000, max_macs=30_000_000) -> Contraction:
+SMALL_EXTENTS = (1, 2, 3, 4, 5, 7, 8, 12, 16, 24, 32, 33, 40, 64, 72, 96, 128)
+LARGE_EXTENTS = (4, 6, 8, 12, 16, 24, 32, 40, 64, 72, 96, 128, 160, 200)
+
+
+def random_contraction(rng, scalar_type, max_out=200_000, max_macs=30_000_000, pool=SMALL_EXTENTS) -> Contraction:
     """A random well-formed contraction: 1-3 modes per group, ragged extents, random memory orders."""
-    pool = [1, 2, 3, 4, 5, 7, 8, 12, 16, 24, 32, 33, 40, 64, 72, 96, 128]
     letters = list("abcdefghi")
     while True:
         nM, nN, nK = (int(rng.integers(1, 4)) for _ in range(3))

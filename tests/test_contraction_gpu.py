@@ -11,7 +11,7 @@ import os
 import numpy as np
 import pytest
 
-from cases import CONFIGS, fixture_contraction, golden_fixtures, random_contraction, to_equation
+from cases import CONFIGS, LARGE_EXTENTS, fixture_contraction, golden_fixtures, random_contraction, to_equation
 from oracle_lib import F32, F64, Contraction
 
 pytestmark = pytest.mark.gpu
@@ -343,6 +343,35 @@ def test_random_descriptors(engine, oracle, seed):
             check(oracle, c, A, B, out, desc)
         except AssertionError as e:
             raise AssertionError(f"{c} selection {sel} -> {desc['backend']}/{desc['kernel']}: {e}") from e
+
+
+@pytest.mark.parametrize("seed", range(2))
+@pytest.mark.parametrize("switch", ["TCONT_KERNEL=gather", "TCONT_KERNEL=tma", "TCONT_KERNEL=simt", "TCONT_SPLITK=3", "TCONT_TF32X3=1",
+                                    "TCONT_UMMA_PAIR=1"])
+def test_random_descriptors_under_switches(engine, oracle, monkeypatch, switch, seed):
+    """The same random descriptors with the planner pushed off its own choice: the gather FP64 kernel, the TMA-fed
+    FP64 kernel wherever it can run, CUDA cores only, three k ranges, the error-compensated Float32 mode, CTA pairs."""
+    key, value = switch.split("=")
+    monkeypatch.setenv(key, value)
+    rng = np.random.default_rng(2000 + seed)
+    for i in range(10):
+        c = random_contraction(rng, (seed + i) % 2, max_out=3_000_000, max_macs=400_000_000, pool=LARGE_EXTENTS)   # sizes the tensor kernels are chosen for
+        sel = int(rng.integers(0, 3))
+        A, B = oracle.inputs(c, 100 * seed + i, -1.0, 1.0)
+        out, desc = run_contraction(engine, c, A, B, sel)
+        try:
+            if c.scalar_type == F32 and (switch == "TCONT_TF32X3=1" or desc["kernel"] != "umma_tf32"):
+                # fp32-level results (CUDA cores, or three compensated tensor-core products): held against the
+                # exact oracle, scaled by sum|a b| because these contracted extents reach tens of thousands
+                exact = oracle.contract(c, A, B, rounding=0)
+                diff, nonfinite = oracle.compare(exact, out, F32)
+                assert diff == 0 and nonfinite == 0, f"{diff} elements outside the reference tolerance"
+                worst = float((np.abs(out.astype(np.float64) - exact) / (tf32_bound(oracle, c, A, B) + 1e-30)).max())
+                assert worst < 2e-5, f"off the exact oracle by {worst:.3e} x sum|ab|"
+            else:
+                check(oracle, c, A, B, out, desc)
+        except AssertionError as e:
+            raise AssertionError(f"{switch}: {c} selection {sel} -> {desc['backend']}/{desc['kernel']}: {str(e)[:300]}") from e
 
 
 @pytest.mark.skipif(os.environ.get("TCONT_TEST_CFG3", "1") != "1", reason="disabled by TCONT_TEST_CFG3")
