@@ -172,3 +172,37 @@ def test_random_descriptors_plan_consistently(engine):
             assert u["eligible"] and u["smem_bytes"] <= 227 * 1024
             assert u["tiles_m"] * u["BM"] >= d["Mtot"] and u["tiles_n"] * u["BN"] >= d["Ntot"]
             assert u["k_iters"] * u["BK"] >= d["Ktot"] and 1 <= u["k_splits"] <= u["k_iters"]
+
+
+def test_planning_is_reentrant(engine):
+    """plan() from eight threads at once (ctypes releases the GIL) gives what a single thread gets, and an error raised
+    in one thread does not leak into another's tcontb_last_error (it is thread-local)."""
+    import threading
+
+    import numpy as np
+
+    from cases import random_contraction
+    rng = np.random.default_rng(5)
+    eqs = [to_equation(engine, random_contraction(rng, i % 2), i % 3) for i in range(40)]
+    want = [engine.plan(e).describe() for e in eqs]
+    bad = engine.TCEquation("ab", "ak", "kb", dict(a=4, b=4))   # extent of k missing
+    failures = []
+
+    def worker(tid):
+        try:
+            for rep in range(5):
+                for i, e in enumerate(eqs):
+                    if (i + tid) % 7 == 0:
+                        with pytest.raises(ValueError, match="k"):
+                            engine.plan(bad)
+                    if engine.plan(e).describe() != want[i]:
+                        failures.append((tid, rep, i))
+        except Exception as ex:  # noqa: BLE001
+            failures.append((tid, repr(ex)))
+
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(8)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not failures, failures[:3]
