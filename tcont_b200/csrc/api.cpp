@@ -70,6 +70,17 @@ struct DeviceBuffer {
     cudaError_t alloc(size_t bytes) { return cudaMalloc(&ptr, bytes ? bytes : 1); }
 };
 
+// Restores the device that was current when a multi-GPU function started, on every way out of it.
+struct DeviceGuard {
+    int device;
+    bool active;
+    explicit DeviceGuard(int d, bool on) : device(d), active(on) {}
+    ~DeviceGuard()
+    {
+        if (active) cudaSetDevice(device);
+    }
+};
+
 }  // namespace
 
 struct tcontb_run {
@@ -197,6 +208,8 @@ void fill_operand_dev(const UmmaOperand& o, UmmaOperandDev* d)
     d->slab_mode_ext = static_cast<int>(o.slab_mode_ext);
     d->total_slabs = o.total_slabs;
     for (int i = 0; i < 3; ++i) d->k_digit_dim[i] = o.k_digit_dim[i];
+    d->split_inner = static_cast<int>(o.split_inner);
+    d->split_outer_cstride = o.split_outer_cstride;
 }
 
 tcontb_status encode_map(const UmmaOperand& o, const void* base, int elt, CUtensorMap* out)
@@ -295,6 +308,11 @@ tcontb_status finish_run(tcontb_run* run)
         run->umma.C64 = static_cast<double*>(out);
         run->umma.status = static_cast<int*>(run->status.ptr);
         run->umma.prof = nullptr;
+        run->umma.wait_limit_ns = 0;
+        run->umma.test_skip_iter = -1;
+        // Test hooks of the bounded-wait exit (tcgen05 kernel only; see UmmaParams).
+        if (const char* e = std::getenv("TCONT_TEST_WAIT_LIMIT_NS")) run->umma.wait_limit_ns = std::strtoull(e, nullptr, 10);
+        if (const char* e = std::getenv("TCONT_TEST_SKIP_STAGE")) run->umma.test_skip_iter = std::atoi(e);
         if (const char* pe = std::getenv("TCONT_UMMA_PROF")) {
             if (pe[0] == '1') {
                 TC_CUDA(run->prof.alloc(static_cast<size_t>(run->num_sms) * 8 * sizeof(long long)));
@@ -312,8 +330,9 @@ tcontb_status finish_run(tcontb_run* run)
             st = encode_map(u.b, run->loB.ptr, u.elt, &run->tmBlo);
             if (st != TCONTB_OK) return st;
         }
-        if (pl.kernel == KERNEL_UMMA_TF32) TC_CUDA(umma_tf32_configure(u.smem_bytes));
-        else TC_CUDA(dmma_tma_configure(u.smem_bytes));
+        if (u.smem_bytes > kMaxDynamicSmemBytes) return fail(TCONTB_RUNTIME_ERROR, "plan asks for more shared memory than a block can have");
+        if (pl.kernel == KERNEL_UMMA_TF32) TC_CUDA(umma_tf32_configure());
+        else TC_CUDA(dmma_tma_configure());
     } else {
         OffsetTables t;
         build_offset_tables(p, &t);
@@ -449,6 +468,7 @@ tcontb_status make_shards(tcontb_run* run, int gpus)
     int have = 0;
     TC_CUDA(cudaGetDeviceCount(&have));
     TC_CUDA(cudaGetDevice(&run->first_device));
+    DeviceGuard guard(run->first_device, true);
     if (run->first_device + gpus > have)
         return fail(TCONTB_RUNTIME_ERROR, "TCONT_NUM_GPUS asks for more devices than the box has from the current device on");
     auto external = [&](char c) {
@@ -582,6 +602,21 @@ tcontb_status build_host_pipeline(tcontb_run* run)
     if (!(run)->shards.empty()) return fail(TCONTB_UNSUPPORTED, what " is not available on a multi-GPU run")
 
 }  // namespace
+
+// A bounded device-side wait that gave up leaves C partly written and only raises the run's status word.
+// The entry points that hand results to the caller synchronise anyway; they read the word there (of the
+// run, its shards and its parts), so that no caller of this C ABI or of the C++ surface above it takes a
+// partial result for a good one.
+static tcontb_status fail_if_device_gave_up(tcontb_run* run)
+{
+    int status = 0;
+    const tcontb_status st = tcontb_run_device_status(run, &status);
+    if (st != TCONTB_OK) return st;
+    if (status != 0)
+        return fail(TCONTB_RUNTIME_ERROR, "a bounded device wait gave up (device status " + std::to_string(status) +
+                                              "): the output tensor is incomplete");
+    return TCONTB_OK;
+}
 
 extern "C" {
 
@@ -743,6 +778,7 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
 {
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
     if (!run->shards.empty()) {
+        DeviceGuard guard(run->first_device, true);
         // Every shard runs on its own device's NULL stream; the first device's NULL stream then waits
         // for all of them, so events the caller records there bracket the whole multi-GPU launch.
         for (size_t g = 0; g < run->shards.size(); ++g) {
@@ -812,6 +848,7 @@ tcontb_status tcontb_run_warmup(tcontb_run* run, int iterations)
         const tcontb_status st = tcontb_run_launch(run);
         if (st != TCONTB_OK) return st;
     }
+    DeviceGuard guard(run->first_device, !run->shards.empty());
     for (size_t g = 0; g < run->shards.size(); ++g) {
         TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
         TC_CUDA(cudaDeviceSynchronize());
@@ -825,6 +862,7 @@ tcontb_status tcontb_run_zero_output(tcontb_run* run)
 {
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
     if (!run->shards.empty()) {
+        DeviceGuard guard(run->first_device, true);
         for (size_t g = 0; g < run->shards.size(); ++g) {
             TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
             const tcontb_status st = tcontb_run_zero_output(run->shards[g].get());
@@ -848,6 +886,10 @@ tcontb_status tcontb_run_stage_times(tcontb_run* run, float out[6])
     TC_CUDA(cudaEventElapsedTime(&ta, run->ev[0], run->ev[1]));
     TC_CUDA(cudaEventElapsedTime(&tb, run->ev[1], run->ev[2]));
     TC_CUDA(cudaEventElapsedTime(&tc, run->ev[2], run->ev[3]));
+    // a route without a transpose reports zero for it (the few microseconds between two events that bracket
+    // nothing are not a stage)
+    if (!run->plan.tA.needed) ta = 0.0f;
+    if (!run->plan.tB.needed) tb = 0.0f;
     out[0] = 1.0f;
     out[1] = ta + tb + tc;
     out[2] = run->plan.prob.swapped ? tb : ta;  // reported per caller operand: left, right
@@ -872,6 +914,7 @@ tcontb_status tcontb_run_copy_output(tcontb_run* run, void* dst, size_t bytes)
     if (!run->shards.empty()) {
         // gather: every shard's C goes back to its slice of the global tensor
         if (bytes != have) return fail(TCONTB_INVALID_ARGUMENT, "A multi-GPU run copies the whole output tensor or nothing");
+        DeviceGuard guard(run->first_device, true);
         const Plan& pl = run->plan;
         const int64_t len = pl.ext_val[pl.ext_mode.find(run->split_mode)] / static_cast<int64_t>(run->shards.size());
         std::vector<unsigned char> part;
@@ -884,11 +927,11 @@ tcontb_status tcontb_run_copy_output(tcontb_run* run, void* dst, size_t bytes)
                        run->elt, true);
         }
         TC_CUDA(cudaSetDevice(run->first_device));
-        return TCONTB_OK;
+        return fail_if_device_gave_up(run);
     }
     TC_CUDA(cudaMemcpyAsync(dst, run->dC, bytes, cudaMemcpyDeviceToHost, run->stream));
     TC_CUDA(cudaStreamSynchronize(run->stream));
-    return TCONTB_OK;
+    return fail_if_device_gave_up(run);
 }
 
 tcontb_status tcontb_run_time_launches(tcontb_run* run, int iterations, float* elapsed_ms, int64_t* kernel_launches)
@@ -957,7 +1000,7 @@ tcontb_status tcontb_run_contract_host(tcontb_run* run, const void* a_host, cons
         TC_CUDA(cudaStreamSynchronize(run->stream));
         if (h2d) *h2d = (pl.sizeL + pl.sizeR) * static_cast<int64_t>(run->elt);
         if (d2h) *d2h = static_cast<int64_t>(pl.sizeC) * static_cast<int64_t>(run->elt);
-        return TCONTB_OK;
+        return fail_if_device_gave_up(run);
     }
     tcontb_status st = tcontb_run_upload_inputs(run, a_host, b_host);
     if (st != TCONTB_OK) return st;
@@ -976,6 +1019,7 @@ tcontb_status tcontb_run_device_status(tcontb_run* run, int* status)
     if (!run || !status) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
     if (!run->shards.empty()) {
         *status = 0;
+        DeviceGuard guard(run->first_device, true);
         for (size_t g = 0; g < run->shards.size(); ++g) {
             int s1 = 0;
             TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));

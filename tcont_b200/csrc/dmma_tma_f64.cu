@@ -297,7 +297,7 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     int d0 = 0;
                     const long long off = slab_c_offset(o, (is_row ? tm * SA : tn * SB) + sl, &d0, &ok);
                     ok = ok && (d0 * o.slab_w + in < o.slab_mode_ext);
-                    st_shared_s64(tab + static_cast<uint32_t>(e) * 8u, ok ? off + in * o.row_elem_cstride : -1);
+                    st_shared_s64(tab + static_cast<uint32_t>(e) * 8u, ok ? off + slab_elem_offset(o, d0, in) : -1);
                 }
                 mbar_arrive(smem_u32(tab_full + slot));
             }
@@ -468,8 +468,9 @@ cudaError_t launch_width(const UmmaParams& p, const void* tmapA, const void* tma
 }
 
 template <int NF>
-cudaError_t configure_width(int smem_bytes)
+cudaError_t configure_width()
 {
+    const int smem_bytes = kMaxDynamicSmemBytes;  // the same opt-in maximum for every run (the cap is per function and device)
     cudaError_t e = cudaFuncSetAttribute(dmma_tma_kernel<false, false, NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<false, true, NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(dmma_tma_kernel<true, false, NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -479,10 +480,10 @@ cudaError_t configure_width(int smem_bytes)
 
 }  // namespace
 
-cudaError_t dmma_tma_configure(int smem_bytes)
+cudaError_t dmma_tma_configure()
 {
-    const cudaError_t e = configure_width<4>(smem_bytes);
-    return e == cudaSuccess ? configure_width<2>(smem_bytes) : e;
+    const cudaError_t e = configure_width<4>();
+    return e == cudaSuccess ? configure_width<2>() : e;
 }
 
 cudaError_t launch_dmma_tma(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms, cudaStream_t stream)

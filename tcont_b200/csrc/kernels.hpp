@@ -52,6 +52,8 @@ struct UmmaOperandDev {
     int slab_mode_ext;
     long long total_slabs;
     int k_digit_dim[3];
+    int split_inner;                // operand-level row fusion: see UmmaOperand (0 = none)
+    long long split_outer_cstride;
 };
 struct UmmaParams {
     UmmaOperandDev a, b;
@@ -70,16 +72,23 @@ struct UmmaParams {
     double* C64;    // TMA-fed FP64 kernel
     int* status;  // device status word: set non-zero when a bounded wait gives up
     long long* prof;  // optional per-CTA cycle counters [grid][8] (TCONT_UMMA_PROF=1), else null
+    // Test hooks of the bounded-wait exit (tcgen05 kernel): a shorter wait limit (0 = the default 2 s), and
+    // the index of one k iteration per CTA whose stage the producer leaves unfilled and unannounced
+    // (-1 = none), so that the MMA warp's wait on it runs out with nothing in flight for that stage.
+    unsigned long long wait_limit_ns;
+    int test_skip_iter;
 };
 // tmapA / tmapB are 128-byte CUtensorMap objects passed by value as kernel parameters.
 cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,
                              cudaStream_t stream);
-cudaError_t umma_tf32_configure(int smem_bytes);
+// Opt-in maximum of dynamic shared memory per block on sm_100 (227 KB); set once per function and device.
+constexpr int kMaxDynamicSmemBytes = 227 * 1024;
+cudaError_t umma_tf32_configure();
 
 // ---- TMA-fed FP64 tensor-path contraction (dmma_tma_f64.cu), same parameter block ------------
 cudaError_t launch_dmma_tma(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,
                             cudaStream_t stream);
-cudaError_t dmma_tma_configure(int smem_bytes);
+cudaError_t dmma_tma_configure();
 
 // ---- split-K: C[e] = sum over s of partial[s * stride + e], s ascending (splitk_reduce.cu) ----
 // With alpha != 1 or beta != 0: C[e] = alpha * sum + beta * C[e] (C is read only when beta != 0).

@@ -13,10 +13,13 @@
 //   * contractions whose tables do not fit are rejected, never truncated;
 //   * all calls share it, so two calls that overlap on the GPU (different streams, or different
 //     host threads) race; calls on one stream are safe;
-//   * it keeps whatever the previous call left; each call overwrites exactly the part it reads,
-//     so nothing needs to start at zero.
+//   * it keeps whatever the previous call left; each call's table kernel overwrites exactly the part
+//     its contraction kernel reads, on the same stream, so nothing needs to start at zero.
+// The tables are computed on the device from per-mode extents and strides passed as kernel arguments:
+// the call copies nothing from host memory and never makes the host wait for the stream.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -33,6 +36,35 @@ constexpr size_t kNoAllocScratchEntries = kNoAllocScratchBytes / sizeof(long lon
 // File-scope device array.  In host code this name is only a handle for the runtime; the device
 // address is obtained with cudaGetSymbolAddress below and that pointer is what the kernel gets.
 static __device__ __align__(256) long long g_no_alloc_tables[kNoAllocScratchEntries];
+
+// Per-mode description of the three index groups (0: rows of A and C, 1: rows of B and C, 2: contracted),
+// passed by value; table entry i of group g is the mixed-radix number i over the group's extents, dotted
+// with the group's strides in its two tensors.
+struct TableSpec {
+    int n_modes[3];
+    long long total[3];
+    long long extent[3][tcontb::kMaxModes];
+    long long stride_x[3][tcontb::kMaxModes];
+    long long stride_y[3][tcontb::kMaxModes];
+    long long* out_x[3];
+    long long* out_y[3];
+};
+
+__global__ void __launch_bounds__(256) fill_offset_tables_kernel(const __grid_constant__ TableSpec s)
+{
+    const int g = blockIdx.y;
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= s.total[g]) return;
+    long long rem = i, x = 0, y = 0;
+    for (int m = 0; m < s.n_modes[g]; ++m) {
+        const long long idx = rem % s.extent[g][m];
+        rem /= s.extent[g][m];
+        x += idx * s.stride_x[g][m];
+        y += idx * s.stride_y[g][m];
+    }
+    s.out_x[g][i] = x;
+    s.out_y[g][i] = y;
+}
 
 constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
@@ -92,20 +124,45 @@ extern "C" tcontb_status tcontb_contract_no_alloc(const tcontb_desc* d, const vo
     cudaError_t e = scratch_for_current_device(&scratch);
     if (e != cudaSuccess) return fail(TCONTB_RUNTIME_ERROR, std::string("cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
 
-    OffsetTables t;
-    build_offset_tables(p, &t);
-    std::vector<long long> flat;
-    flat.reserve(need);
-    size_t at[6];
-    const std::vector<int64_t>* src[6] = {&t.offAm, &t.offAk, &t.offBn, &t.offBk, &t.offCm, &t.offCn};
-    for (int i = 0; i < 6; ++i) {
-        at[i] = flat.size();
-        flat.insert(flat.end(), src[i]->begin(), src[i]->end());
-    }
+    // The six tables are written by a small kernel on the caller's stream from the per-mode extents and
+    // strides, which travel by value as kernel arguments: no host buffer outlives this call, the host does
+    // not wait for earlier work on the stream, and the contraction kernel behind it sees finished tables.
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-    // Pageable source: the runtime has taken its copy of `flat` by the time this call returns.
-    e = cudaMemcpyAsync(scratch, flat.data(), flat.size() * sizeof(long long), cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return fail(TCONTB_RUNTIME_ERROR, std::string("table upload failed: ") + cudaGetErrorString(e));
+    TableSpec spec{};
+    const std::vector<int>* groups[3] = {&p.M, &p.N, &p.K};
+    const int64_t totals[3] = {p.Mtot, p.Ntot, p.Ktot};
+    size_t at[6];
+    {
+        // order in the array: offAm, offAk, offBn, offBk, offCm, offCn
+        const size_t len[6] = {size_t(p.Mtot), size_t(p.Ktot), size_t(p.Ntot), size_t(p.Ktot), size_t(p.Mtot), size_t(p.Ntot)};
+        size_t pos = 0;
+        for (int i = 0; i < 6; ++i) {
+            at[i] = pos;
+            pos += len[i];
+        }
+    }
+    for (int g = 0; g < 3; ++g) {
+        spec.n_modes[g] = static_cast<int>(groups[g]->size());
+        spec.total[g] = totals[g];
+        for (size_t i = 0; i < groups[g]->size() && i < static_cast<size_t>(kMaxModes); ++i) {
+            const Mode& m = p.modes[static_cast<size_t>((*groups[g])[i])];
+            spec.extent[g][i] = m.extent;
+            // M rows index A and C, N rows index B and C, K indexes A and B
+            spec.stride_x[g][i] = g == 0 ? m.sA : g == 1 ? m.sB : m.sA;
+            spec.stride_y[g][i] = g == 0 ? m.sC : g == 1 ? m.sC : m.sB;
+        }
+    }
+    spec.out_x[0] = scratch + at[0];  // offAm
+    spec.out_y[0] = scratch + at[4];  // offCm
+    spec.out_x[1] = scratch + at[2];  // offBn
+    spec.out_y[1] = scratch + at[5];  // offCn
+    spec.out_x[2] = scratch + at[1];  // offAk
+    spec.out_y[2] = scratch + at[3];  // offBk
+    const int64_t longest = std::max(p.Mtot, std::max(p.Ntot, p.Ktot));
+    const dim3 grid(static_cast<unsigned>((longest + 255) / 256), 3);
+    fill_offset_tables_kernel<<<grid, 256, 0, stream>>>(spec);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(TCONTB_RUNTIME_ERROR, std::string("table kernel launch failed: ") + cudaGetErrorString(e));
 
     const int64_t* base = reinterpret_cast<const int64_t*>(scratch);
     SimtParams sp{};

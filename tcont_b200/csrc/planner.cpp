@@ -62,6 +62,16 @@ int build_problem(const std::string& mC, const std::string& mL, const std::strin
             *err = "A mode appears twice in one tensor (traces/diagonals are not expressible)";
             return 3;
         }
+        // Element counts are products of caller-supplied 64-bit extents: multiply with an overflow check
+        // before anything derives strides, table sizes or allocations from them.
+        int64_t n = 1;
+        for (char c : *s) {
+            const int64_t e = extent_of(c);
+            if (e >= (int64_t(1) << 31) || __builtin_mul_overflow(n, e, &n) || n >= (int64_t(1) << 40)) {
+                *err = "Tensor too large: extents must stay below 2^31 and a tensor below 2^40 elements";
+                return 3;
+            }
+        }
     }
     // C's stride-1 mode decides which caller operand plays role A.
     p.swapped = !mC.empty() && find_char(mL, mC[0]) < 0 && find_char(mR, mC[0]) >= 0;

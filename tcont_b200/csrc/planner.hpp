@@ -72,6 +72,12 @@ struct UmmaOperand {
     int64_t total_slabs = 1;
     int k_digit_dim[3] = {-1, -1, -1};
     int slab_bytes = 0;
+    // Operand-level row fusion (FP64 kernel): the slab mode is two row modes that lie one after the other in
+    // the operand but not in C (a short stride-1 mode and the next one), shown to TMA as one dimension.
+    // Position q of the fused mode sits at (q % split_inner) * row_elem_cstride + (q / split_inner) *
+    // split_outer_cstride in C.  0 = not fused.
+    int64_t split_inner = 0;
+    int64_t split_outer_cstride = 0;
 };
 
 struct UmmaSpec {

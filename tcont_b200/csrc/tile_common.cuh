@@ -89,8 +89,11 @@ __device__ __forceinline__ long long ld_shared_s64(uint32_t addr)
 // flag, when the limit passes; returns false at once when another thread already gave up.
 // `sleep_ns` > 0: the thread sleeps that long after a failed poll, for warps whose polling would
 // otherwise take issue slots from the warps doing the arithmetic on the same scheduler.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_addr, uint32_t sleep_ns = 0)
+// `limit_ns` = 0 means the default limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_addr, uint32_t sleep_ns = 0,
+                                          unsigned long long limit_ns = 0)
 {
+    const unsigned long long limit = limit_ns ? limit_ns : kWaitLimitNs;
     unsigned long long t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -100,7 +103,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
             if (spin == 0) continue;
             const unsigned long long now = global_timer();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) {
+            else if (now - t0 > limit) {
                 st_shared_u32(abort_addr, 1u);
                 return false;
             }
@@ -165,6 +168,19 @@ __device__ __forceinline__ long long slab_c_offset(const UmmaOperandDev& o, uint
         }
     }
     return off;
+}
+
+// C offset of position `in` of a slab whose digit-0 index is `digit0`, relative to what slab_c_offset returned.
+// With operand-level row fusion (split_inner > 0) the slab mode is two C modes, and digit 0 carries no C
+// stride of its own: the position inside the fused mode is split here.
+__device__ __forceinline__ long long slab_elem_offset(const UmmaOperandDev& o, int digit0, int in)
+{
+    if (o.split_inner > 0) {
+        const int pos = digit0 * o.slab_w + in;
+        return static_cast<long long>(pos % o.split_inner) * o.row_elem_cstride +
+               static_cast<long long>(pos / o.split_inner) * o.split_outer_cstride;
+    }
+    return static_cast<long long>(in) * o.row_elem_cstride;
 }
 
 }  // namespace

@@ -217,6 +217,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         uint32_t phase = 0;
         uint32_t issued_mask = 0, issued_parity = 0;
         long long t_empty = 0;
+        int cta_iter = 0;  // k iterations this CTA has gone through (test hook: one of them may be left out)
 
         for (uint32_t tile = first_unit; tile < total_tiles; tile += unit_step) {
             const WorkUnit w = decode_unit(tile, p, tiles_m, tiles_n);
@@ -249,11 +250,11 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             // K digits: chunk of the chunked mode, then the other K modes
             int kd0 = w.it0 % p.k_digit_ext[0], kd1 = (w.it0 / p.k_digit_ext[0]) % p.k_digit_ext[1];
             int kd2 = w.it0 / (p.k_digit_ext[0] * p.k_digit_ext[1]);
-            for (int it = 0; it < w.n_it; ++it) {
+            for (int it = 0; it < w.n_it; ++it, ++cta_iter) {
                 const long long t0 = p.prof ? clock64() : 0;
-                const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + stage), phase ^ 1u, abort_flag));
+                const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + stage), phase ^ 1u, abort_flag, 0, p.wait_limit_ns));
                 if (p.prof) t_empty += clock64() - t0;
-                if (ok) {
+                if (ok && cta_iter != p.test_skip_iter) {
                     // one arrival with the byte count of the whole stage; in a pair the MMA-issuing CTA
                     // accounts for both CTAs' copies, which all signal its barrier
                     if (lane == 0 && rank == 0) mbar_arrive_expect_tx(smem_u32(bar_full + stage), PAIR ? 2u * stage_bytes : stage_bytes);
@@ -321,14 +322,14 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                 const int acc = static_cast<int>(iter & 1);
                 const uint32_t acc_parity = static_cast<uint32_t>((iter >> 1) & 1);
                 long long t0 = p.prof ? clock64() : 0;
-                bool ok = mbar_wait(smem_u32(bar_tempty + acc), acc_parity ^ 1u, abort_flag);
+                bool ok = mbar_wait(smem_u32(bar_tempty + acc), acc_parity ^ 1u, abort_flag, 0, p.wait_limit_ns);
                 if (p.prof) t_tempty += clock64() - t0;
                 tcgen05_fence_after();
                 const uint32_t tmem_c = tmem_base + static_cast<uint32_t>(acc * p.BN);
                 const int n_it = decode_unit(tile, p, tiles_m, tiles_n).n_it;
                 for (int it = 0; it < n_it; ++it) {
                     t0 = p.prof ? clock64() : 0;
-                    ok = ok && mbar_wait(smem_u32(bar_full + stage), phase, abort_flag);
+                    ok = ok && mbar_wait(smem_u32(bar_full + stage), phase, abort_flag, 0, p.wait_limit_ns);
                     if (p.prof) t_full += clock64() - t0;
                     if (ok) {
                         tcgen05_fence_after();
@@ -421,7 +422,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             };
             bool ok = true;
             const long long t0 = p.prof ? clock64() : 0;
-            if (lane == 0) ok = mbar_wait(smem_u32(bar_tfull + acc), acc_parity, abort_flag);
+            if (lane == 0) ok = mbar_wait(smem_u32(bar_tfull + acc), acc_parity, abort_flag, 0, p.wait_limit_ns);
             if (p.prof) t_tfull += clock64() - t0;
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             tcgen05_fence_after();
@@ -502,11 +503,13 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
 
 }  // namespace
 
-cudaError_t umma_tf32_configure(int smem_bytes)
+// The dynamic shared-memory cap is a property of the function on a device, not of a run: every run sets
+// the same opt-in maximum, so runs with different stage counts can live side by side.
+cudaError_t umma_tf32_configure()
 {
-    cudaError_t e = cudaFuncSetAttribute(umma_tf32_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    cudaError_t e = cudaFuncSetAttribute(umma_tf32_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmemBytes);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(umma_tf32_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    return cudaFuncSetAttribute(umma_tf32_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmemBytes);
 }
 
 cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,

@@ -1,5 +1,4 @@
-"""CPU-only checks of bench.py's host logic: the clock record built from nvidia-smi samples."""
-import datetime
+"""CPU-only checks of bench.py's host logic: the clock record built from NVML samples."""
 import importlib.util
 import os
 
@@ -13,22 +12,27 @@ def _bench():
     return mod
 
 
-def _line(t, index, sm, cap):
-    stamp = datetime.datetime.fromtimestamp(t).strftime("%Y/%m/%d %H:%M:%S.%f")[:-3]
-    return f"{stamp}, {index}, {sm}, 1965, 700.00, 0x0000000000000004, Not Active, Not Active, Not Active, {'Active' if cap else 'Not Active'}\n"
-
-
-def test_clock_samples_split_at_the_end_of_the_timed_region():
+def test_clock_samples_are_attributed_to_the_timed_regions():
     bench = _bench()
     t0 = 1_800_000_000.0
-    lines = [_line(t0 + 0.0, 0, 1965, False), _line(t0 + 0.1, 0, 1950, False),      # timed region
-             _line(t0 + 0.1, 1, 300, True),                                          # another GPU: ignored
-             _line(t0 + 0.3, 0, 1700, True), _line(t0 + 0.4, 0, 1690, True),        # untimed repeats reach the power cap
-             "garbage\n"]
-    c = bench.summarise_clock_samples(lines, {0}, t_mark=t0 + 0.2)
-    assert c["samples"] == 4 and c["samples_in_timed_region"] == 2
-    assert c["reasons"] == ["sw_power_cap"] and c["reasons_in_timed_region"] == []
-    assert c["sm_max_mhz"] == 1965.0 and c["sm_mhz"] == 1957.5   # median of the upper half
-    c = bench.summarise_clock_samples(lines, {0}, t_mark=t0 + 1.0)
-    assert c["reasons_in_timed_region"] == ["sw_power_cap"]
-    assert bench.summarise_clock_samples([], {0})["sm_mhz"] is None
+    cap = 0x4
+    samples = [(t0 + 0.00, 0, 1965.0, 1965.0, 600.0, 0), (t0 + 0.01, 0, 1950.0, 1965.0, 700.0, 0),     # headline timed region
+               (t0 + 0.01, 1, 1900.0, 1965.0, 650.0, 0),
+               (t0 + 0.30, 0, 1700.0, 1965.0, 990.0, cap), (t0 + 0.40, 0, 1690.0, 1965.0, 995.0, cap),   # untimed repeats reach the power cap
+               (t0 + 0.50, 0, 1800.0, 1965.0, 800.0, 0x20)]                                              # a sub-record's region
+    c = bench.summarise_clock_samples(samples, {"headline": (t0, t0 + 0.05), "cfg2": (t0 + 0.45, t0 + 0.55)})
+    assert c["samples"] == 6 and c["samples_in_timed_region"] == 3
+    assert c["reasons"] == ["sw_power_cap", "sw_thermal_slowdown"] and c["reasons_in_timed_region"] == []
+    assert c["sm_max_mhz"] == 1965.0 and c["sm_mhz_in_timed_region"] == 1950.0
+    assert c["windows"]["cfg2"]["samples"] == 1 and c["windows"]["cfg2"]["reasons"] == ["sw_thermal_slowdown"]
+    assert c["power_w_max"] == 995.0
+    empty = bench.summarise_clock_samples([], {"headline": (t0, t0 + 1)})
+    assert empty["sm_mhz"] is None and empty["samples_in_timed_region"] == 0
+
+
+def test_default_workload_is_the_sharded_large_contraction():
+    bench = _bench()
+    w = bench.WORKLOADS["cfg5"]
+    assert w["strong"] == "a" and w["ext"] == dict(a=128, b=128, c=128, d=128, e=128, f=128)
+    assert bench.WORKLOADS["cfg3"]["strong"] == "a"
+    assert {s[0] for s in bench.SUB_RECORDS} == {"cfg2", "cfg3", "cfg4"}

@@ -16,6 +16,15 @@ from oracle_lib import F32, F64, Contraction
 
 pytestmark = pytest.mark.gpu
 FIXTURES = golden_fixtures()
+# Share of the outputs a single TF32 pass may leave outside the reference's Float32 criterion on signed inputs
+# (emulated with truncated operands and exact accumulation: 0.05 % at a contracted extent of 128, 0.29 % at
+# 1 024, 0.34 % at 16 384, none at 8).  Small test tensors get two standard deviations and two elements on top,
+# so that a handful of unlucky outputs among a few hundred does not fail a test.
+TF32_FORMAT_ERROR_FRACTION = 0.005
+
+
+def tf32_outlier_allowance(n: int) -> float:
+    return TF32_FORMAT_ERROR_FRACTION * n + 2.0 * (TF32_FORMAT_ERROR_FRACTION * n) ** 0.5 + 2.0
 
 
 def run_contraction(engine, c, A, B, selection=0, launches=1):
@@ -48,8 +57,11 @@ def check(oracle, c, A, B, out, desc):
         err = np.abs(out.astype(np.float64) - trunc)
         worst = float((err / (scale + 1e-30)).max())
         assert worst < 2e-5, f"tensor-core result is off the TF32-operand oracle by {worst:.3e} x sum|ab|"
-        # the reference criterion against the double oracle can only fail through TF32 format error
-        assert diff <= 0.01 * out.size
+        # The reference criterion against the double oracle can only fail through TF32 format error: on signed
+        # inputs a single TF32 pass leaves up to about 0.3 % of the outputs outside it (those near zero, where
+        # only the absolute term applies), whatever kernel computes it.  Held to 0.5 %, count reported.
+        print(f"[tf32 format error] {diff} of {out.size} outputs ({100.0 * diff / out.size:.3f} %) outside the reference criterion")
+        assert diff <= tf32_outlier_allowance(out.size), f"{diff} of {out.size} outputs outside the reference criterion"
     else:
         assert diff == 0, f"{diff} elements outside the reference tolerance (simt fp32)"
         np.testing.assert_allclose(out, exact, rtol=2e-4, atol=1e-4)
@@ -207,7 +219,9 @@ def _sampled_check(engine, oracle, name, n_samples, selection=0):
             scale = oracle.contract_sampled(c, np.abs(A), np.abs(B), idx, rounding=1)
             worst = float((np.abs(got - trunc) / (scale + 1e-30)).max())
             assert worst < 2e-5, worst
-            assert diff <= 0.01 * n_samples   # TF32 format error on signed inputs, never a kernel error
+            # TF32 format error on signed inputs, never a kernel error (see check())
+            print(f"[tf32 format error] {name}: {diff} of {n_samples} sampled outputs ({100.0 * diff / n_samples:.3f} %) outside the reference criterion")
+            assert diff <= tf32_outlier_allowance(n_samples), f"{diff} of {n_samples} sampled outputs outside the reference criterion"
         else:
             assert diff == 0
     assert np.isfinite(out).all()
@@ -431,3 +445,59 @@ def test_host_buffer_path(engine, oracle, monkeypatch, c, chunks):
         check(oracle, c, A, B, out, p.describe())
     assert r.device_status() == 0
     np.testing.assert_array_equal(engine.copy_output_to_host(r), out)   # the device copy of C is whole as well
+
+
+SIDE_BY_SIDE = {
+    # two plans of one kernel family whose dynamic shared memory differs: (large, small, backend selection)
+    "tf32": (Contraction("ab", "ak", "kb", dict(a=4096, b=1280, k=64), F32), UMMA_SHAPES["cfg5_like"], 0),
+    "fp64": (FP64_SHAPES["gemm_mn_k"], FP64_SHAPES["slab8_k8"], 1),
+}
+
+
+@pytest.mark.parametrize("family", list(SIDE_BY_SIDE))
+def test_runs_with_different_shared_memory_side_by_side(engine, oracle, family):
+    """The dynamic shared-memory cap belongs to the kernel function on a device, not to a run: a run created
+    later with a smaller stage ring must not lower it under a run created earlier.  Both runs stay alive and
+    are launched alternately."""
+    big, small, sel = SIDE_BY_SIDE[family]
+    runs = []
+    for c in (big, small):
+        A, B = oracle.inputs(c, 55, -1.0, 1.0)
+        p = engine.plan(to_equation(engine, c, sel))
+        runs.append((c, A, B, p, engine.prepare(p, A, B)))
+    smem = [r[3].describe()["umma"]["smem_bytes"] for r in runs]
+    assert smem[0] > smem[1], smem
+    for i in (0, 1, 0, 1, 0):
+        c, A, B, p, r = runs[i]
+        engine.zero_output(r)
+        engine.launch(r)
+        out = engine.copy_output_to_host(r)
+        assert r.device_status() == 0
+        check(oracle, c, A, B, out, p.describe())
+
+
+def test_bounded_wait_gives_up_cleanly(engine, oracle, monkeypatch):
+    """The exit every device-side wait has: with the test hook the producer leaves one stage of the ring
+    unannounced and unfilled (nothing in flight for it), so the MMA warp's wait on that stage runs out after
+    the shortened limit.  The kernel must return, raise the run's status word, and leave the context usable:
+    the entry point that hands out results reports a runtime error, and an ordinary run right after it is
+    correct.  Nothing faults and nothing is left spinning."""
+    import torch
+    from tcont_b200 import api
+    c = UMMA_SHAPES["cfg2_like"]
+    A, B = oracle.inputs(c, 9, -1.0, 1.0)
+    p = engine.plan(to_equation(engine, c, 0))
+    assert p.describe()["kernel"] == "umma_tf32"
+    monkeypatch.setenv("TCONT_TEST_WAIT_LIMIT_NS", "2000000")    # 2 ms instead of 2 s
+    monkeypatch.setenv("TCONT_TEST_SKIP_STAGE", "1")             # every CTA's second k iteration never arrives
+    broken = engine.prepare(p, A, B)
+    monkeypatch.delenv("TCONT_TEST_WAIT_LIMIT_NS")
+    monkeypatch.delenv("TCONT_TEST_SKIP_STAGE")
+    engine.launch(broken)
+    torch.cuda.synchronize()                                     # no error from the runtime
+    assert broken.device_status() == 1
+    with pytest.raises(api.TcontError, match="bounded device wait gave up"):
+        engine.copy_output_to_host(broken)
+    del broken
+    out, desc = run_contraction(engine, c, A, B, 0)              # the same contraction on a fresh run
+    check(oracle, c, A, B, out, desc)

@@ -38,12 +38,17 @@ def _both(engine, oracle, c):
     engine.launch(run)
     stream = torch.cuda.current_stream().cuda_stream
     outs = []
-    for _ in range(2):   # two calls in a row through the allocation-free entry point
+    for call in range(2):   # two calls in a row through the allocation-free entry point
         c_noalloc.fill_(float("nan"))
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        # free device memory as the driver counts it (cudaMemGetInfo): sees any allocation, whoever makes it,
+        # not only those of torch's caching allocator
+        free_before, _ = torch.cuda.mem_get_info()
         api.contract_no_alloc(eq, dA.data_ptr(), dB.data_ptr(), c_noalloc.data_ptr(), stream)
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        free_after, _ = torch.cuda.mem_get_info()
+        if call == 1:   # (the first call on a device may load the kernels' module)
+            assert free_after == free_before, f"device memory changed by {free_before - free_after} bytes across the call"
         outs.append(c_noalloc.cpu().numpy().copy())
     return c_regular.cpu().numpy(), outs, (A, B)
 
@@ -57,6 +62,26 @@ def test_no_alloc_matches_regular_entry_point(engine, oracle, c):
         assert (diff, nonfinite) == (0, 0)
         diff, nonfinite = oracle.compare(oracle.contract(c, A, B), got, c.scalar_type)
         assert (diff, nonfinite) == (0, 0)
+
+
+def test_no_alloc_size_limit_is_exact(engine, oracle):
+    """2*(M+N+K) = 524288 entries is the last size that fits the built-in scratch: accepted and correct;
+    one row more is rejected before any device work."""
+    import torch
+    from tcont_b200 import api
+    c = Contraction("ab", "ak", "kb", dict(a=262000, b=136, k=8), F64)
+    assert 2 * (262000 + 136 + 8) == 524288
+    A, B = oracle.inputs(c, 4, -1.0, 1.0)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.full((c.size(c.modeC),), float("nan"), dtype=torch.float64, device="cuda")
+    eq = engine.TCEquation(c.modeC, c.modeA, c.modeB, dict(c.extent))
+    api.contract_no_alloc(eq, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    diff, nonfinite = oracle.compare(oracle.contract(c, A, B), dC.cpu().numpy(), F64)
+    assert (diff, nonfinite) == (0, 0)
+    over = engine.TCEquation("ab", "ak", "kb", dict(a=262001, b=136, k=8))
+    with pytest.raises(NotImplementedError, match="too large for the allocation-free entry point"):
+        api.contract_no_alloc(over, dA.data_ptr(), dB.data_ptr(), dC.data_ptr())
 
 
 def test_no_alloc_rejects_oversized_contractions(engine):
