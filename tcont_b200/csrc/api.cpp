@@ -128,7 +128,25 @@ struct tcontb_run {
     std::vector<std::unique_ptr<tcontb_run>> shards;
     std::vector<cudaEvent_t> shard_done;
     int first_device = 0;
+    bool one_device = false;  // test mode (TCONT_SHARDS_ON_ONE_DEVICE=1): every shard lives on the first device
     char split_mode = 0;
+    bool split_contracted = false;        // the shards cut a contracted mode (TCONT_SPLIT=k:<mode>)
+    std::vector<cudaEvent_t> shard_kernel;  // shard g's contraction kernel of the current launch has finished
+    int shard_device(size_t g) const { return one_device ? first_device : first_device + static_cast<int>(g); }
+    // Contracted-mode split (tcontb_run_ksplit_*): this run contracts its slice of a contracted mode into a
+    // partial C that never exists as a whole.  C is cut into `world` contiguous ranges along its slowest mode;
+    // the kernel stores the tile columns of range o straight into slot [set][rank] of the staging area of the
+    // GPU that owns range o (its own, or a peer's over NVLink), and the owner sums its `world` slots.
+    // Two sets of slots alternate between launches, so that one barrier per launch (every rank's kernel done
+    // before any rank's sum) is all the ordering the ranks need.
+    struct KSplit {
+        int world = 0, rank = 0;
+        int64_t chunk = 0;                    // elements of one range
+        DeviceBuffer staging;                 // [2 sets][world slots][chunk]
+        void* peer[kMaxOwners] = {nullptr};   // every rank's staging area as this process sees it
+        bool opened[kMaxOwners] = {false};    // mapped through an IPC handle (closed with the run)
+        int set = 0, last_set = 0;
+    } ks;
     // Pipelined host-buffer pass (tcontb_run_contract_host): when C's slowest mode is external and is
     // also the slowest mode of the operand that carries it, a slice of that mode is a contiguous range
     // of the operand and of C.  The contraction is then cut into `parts` along it, each an ordinary
@@ -146,10 +164,13 @@ struct tcontb_run {
 
     ~tcontb_run()
     {
+        for (int o = 0; o < kMaxOwners; ++o)
+            if (ks.opened[o] && ks.peer[o]) cudaIpcCloseMemHandle(ks.peer[o]);
         for (size_t g = 0; g < shards.size(); ++g) {
-            cudaSetDevice(first_device + static_cast<int>(g));
+            cudaSetDevice(shard_device(g));
             shards[g].reset();
             if (g < shard_done.size() && shard_done[g]) cudaEventDestroy(shard_done[g]);
+            if (g < shard_kernel.size() && shard_kernel[g]) cudaEventDestroy(shard_kernel[g]);
         }
         if (!shard_done.empty()) cudaSetDevice(first_device);
         if (prof.ptr) {
@@ -198,6 +219,7 @@ void fill_operand_dev(const UmmaOperand& o, UmmaOperandDev* d)
     d->slab_bytes = o.slab_bytes;
     d->slabs_per_op = o.slabs_per_op;
     d->digit0_scale = o.digit0_scale;
+    d->k0_scale = o.k0_scale;
     d->oob_coord = o.oob_coord;
     for (int i = 0; i < kMaxTmaRank; ++i) {
         d->row_digit_dim[i] = i < o.n_row_digits ? o.row_digit_dim[i] : -1;
@@ -492,7 +514,7 @@ tcontb_status make_shards(tcontb_run* run, int gpus)
     local_ext[pl.ext_mode.find(mode)] = len;
     const bool in_a = pl.modeA.find(mode) != std::string::npos;
     for (int g = 0; g < gpus; ++g) {
-        TC_CUDA(cudaSetDevice(run->first_device + g));
+        TC_CUDA(cudaSetDevice(run->shard_device(static_cast<size_t>(g))));
         std::unique_ptr<tcontb_run> sh(new tcontb_run());
         std::string err;
         const int rc = make_plan(pl.modeC.data(), static_cast<int>(pl.modeC.size()), pl.modeA.data(), static_cast<int>(pl.modeA.size()),
@@ -782,7 +804,7 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
         // Every shard runs on its own device's NULL stream; the first device's NULL stream then waits
         // for all of them, so events the caller records there bracket the whole multi-GPU launch.
         for (size_t g = 0; g < run->shards.size(); ++g) {
-            TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
+            TC_CUDA(cudaSetDevice(run->shard_device(g)));
             const tcontb_status st = tcontb_run_launch(run->shards[g].get());
             if (st != TCONTB_OK) {
                 cudaSetDevice(run->first_device);
@@ -850,7 +872,7 @@ tcontb_status tcontb_run_warmup(tcontb_run* run, int iterations)
     }
     DeviceGuard guard(run->first_device, !run->shards.empty());
     for (size_t g = 0; g < run->shards.size(); ++g) {
-        TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
+        TC_CUDA(cudaSetDevice(run->shard_device(g)));
         TC_CUDA(cudaDeviceSynchronize());
     }
     if (!run->shards.empty()) TC_CUDA(cudaSetDevice(run->first_device));
@@ -864,7 +886,7 @@ tcontb_status tcontb_run_zero_output(tcontb_run* run)
     if (!run->shards.empty()) {
         DeviceGuard guard(run->first_device, true);
         for (size_t g = 0; g < run->shards.size(); ++g) {
-            TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
+            TC_CUDA(cudaSetDevice(run->shard_device(g)));
             const tcontb_status st = tcontb_run_zero_output(run->shards[g].get());
             if (st != TCONTB_OK) return st;
         }
@@ -921,7 +943,7 @@ tcontb_status tcontb_run_copy_output(tcontb_run* run, void* dst, size_t bytes)
         for (size_t g = 0; g < run->shards.size(); ++g) {
             tcontb_run* sh = run->shards[g].get();
             part.resize(static_cast<size_t>(sh->plan.sizeC) * run->elt);
-            TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
+            TC_CUDA(cudaSetDevice(run->shard_device(g)));
             TC_CUDA(cudaMemcpy(part.data(), sh->dC, part.size(), cudaMemcpyDeviceToHost));
             slice_mode(static_cast<unsigned char*>(dst), part.data(), pl.modeC, pl, run->split_mode, static_cast<int64_t>(g) * len, len,
                        run->elt, true);
@@ -1022,7 +1044,7 @@ tcontb_status tcontb_run_device_status(tcontb_run* run, int* status)
         DeviceGuard guard(run->first_device, true);
         for (size_t g = 0; g < run->shards.size(); ++g) {
             int s1 = 0;
-            TC_CUDA(cudaSetDevice(run->first_device + static_cast<int>(g)));
+            TC_CUDA(cudaSetDevice(run->shard_device(g)));
             const tcontb_status st = tcontb_run_device_status(run->shards[g].get(), &s1);
             if (st != TCONTB_OK) return st;
             if (s1 > *status) *status = s1;

@@ -42,9 +42,12 @@ bool make_transpose_params(int rank, const int64_t* src_extent, const int* perm,
 cudaError_t launch_transpose(const void* src, void* dst, const TransposeParams& p, int elem_bytes, cudaStream_t stream);
 
 // ---- TF32 tcgen05 contraction (umma_tf32.cu) -------------------------------------------------
+constexpr int kMaxOwners = 8;  // GPUs of one box
+
 struct UmmaOperandDev {
     int major, slab_w, slabs_per_tile, n_row_digits, slab_bytes;
     int slabs_per_op, digit0_scale, oob_coord;
+    int k0_scale;  // TMA coordinate of k digit 0 = k iteration * this
     int row_digit_dim[kMaxTmaRank];
     int row_digit_ext[kMaxTmaRank];
     long long row_digit_cstride[kMaxTmaRank];
@@ -77,6 +80,13 @@ struct UmmaParams {
     // (-1 = none), so that the MMA warp's wait on it runs out with nothing in flight for that stage.
     unsigned long long wait_limit_ns;
     int test_skip_iter;
+    // Contracted-mode split over several GPUs (tcgen05 kernel): this GPU's partial C is cut into `owners`
+    // contiguous ranges along C's slowest mode, `tn_per_owner` tile columns each, and range o is stored straight
+    // into the memory of the GPU that owns it, over NVLink: element i of the full C (i inside range o) goes to
+    // owner_base[o][i].  owners = 0 or 1: everything goes to C.  `tn_rotate` shifts the order in which a GPU
+    // visits the tile columns, so that the GPUs of a job write to different owners at any one time.
+    int owners, tn_per_owner, tn_rotate;
+    float* owner_base[kMaxOwners];
 };
 // tmapA / tmapB are 128-byte CUtensorMap objects passed by value as kernel parameters.
 cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,

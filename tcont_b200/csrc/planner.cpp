@@ -278,6 +278,7 @@ void finish_operand(const Problem& p, const std::vector<int>& t, const std::vect
         o->slab_bytes = o->slab_w * BK * elt;
     }
     o->slabs_per_op = 1;
+    o->k0_scale = BK;
     o->digit0_scale = o->slab_w;
     o->oob_coord = static_cast<int>(ceil_div(o->slab_mode_ext, W) * W);  // (any coordinate past the mode's end)
 }
@@ -326,10 +327,69 @@ void merge_slabs(UmmaOperand* o, int BK, int cta_slabs)
     *o = n;
 }
 
-void plan_umma(const Problem& p, const CostTable& cost, UmmaSpec* u)
+// How much slabs of 16 or 8 doubles pad a stride-1 mode of extent e.
+double slab_padding_f64(int64_t e)
+{
+    return double(std::min(ceil_div(e, 16) * 16, ceil_div(e, 8) * 8)) / double(e);
+}
+
+// K-major operand with a k chunk of 64 (two 128-byte rows of k per tile row): the chunked mode is shown to TMA
+// as two dimensions (32 contiguous elements, extent / 32 chunks), the chunk dimension last, so that ONE copy
+// with box {32, rows, ..., 2} lands the two 32-wide K chunks of the slab one after the other, each a canonical
+// K-major tile of `rows` x 128 bytes.  Needs a free tensor-map dimension, an extent that is a multiple of 32
+// (a ragged last chunk would read the next row's elements instead of zeros) and one slab per CTA (the rows of
+// a chunk must be contiguous in shared memory for the MMA descriptor).
+bool chunk_kmajor(UmmaOperand* o, int BK, int cta_slabs)
+{
+    if (o->major != 0 || BK <= 32) return true;
+    if (o->rank >= kMaxTmaRank || o->kc_dim != 0 || o->ext[0] % 32 || cta_slabs != 1) return false;
+    const int r = o->rank;
+    o->ext[r] = o->ext[0] / 32;
+    o->stride[r] = 32;
+    o->box[r] = BK / 32;
+    o->ext[0] = 32;
+    o->box[0] = 32;
+    o->rank = r + 1;
+    o->k_digit_dim[0] = r;
+    o->k0_scale = BK / 32;
+    return true;
+}
+
+void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int bk_request)
 {
     u->eligible = false;
-    const bool f64 = p.scalar_type == 1;
+    const bool f64 = p_in.scalar_type == 1;
+    // Operand-level row fusion (FP64 kernel, whose epilogue takes every row's C offset from a table): when the
+    // stride-1 mode of an MN-major operand is so short that whole slabs would pad it by over 8 % (extent 6:
+    // a quarter of every 8-row slab empty) and the next row mode in C's order follows it directly in the
+    // operand, the two are staged as ONE mode: TMA sees a single dimension of the fused extent, tiles have no
+    // empty rows, and the table builder splits a row's position back into the two C modes.
+    Problem p = p_in;
+    int64_t split_inner[2] = {0, 0}, split_outer_cstride[2] = {0, 0};
+    if (f64 && !std::getenv("TCONT_NO_ROW_FUSION")) {
+        for (int which = 0; which < 2; ++which) {
+            std::vector<int>& t = which == 0 ? p.A : p.B;
+            std::vector<int>& rows = which == 0 ? p.M : p.N;
+            if (t.size() < 3 || rows.size() < 2 || t[0] != rows[0] || t[1] != rows[1]) continue;
+            const Mode m0 = p.modes[static_cast<size_t>(t[0])], m1 = p.modes[static_cast<size_t>(t[1])];
+            if (slab_padding_f64(m0.extent) <= 1.08) continue;
+            Mode f;
+            f.names = m0.names + m1.names;
+            f.extent = m0.extent * m1.extent;
+            f.group = m0.group;
+            f.sA = m0.sA;
+            f.sB = m0.sB;
+            f.sC = m0.sC;
+            const int id = static_cast<int>(p.modes.size());
+            p.modes.push_back(f);
+            split_inner[which] = m0.extent;
+            split_outer_cstride[which] = m1.sC;
+            t[0] = id;
+            t.erase(t.begin() + 1);
+            rows[0] = id;
+            rows.erase(rows.begin() + 1);
+        }
+    }
     const int elt = f64 ? 8 : 4, W = 128 / elt;
     u->elt = elt;
     if (const char* k = std::getenv("TCONT_KERNEL")) {
@@ -385,6 +445,13 @@ void plan_umma(const Problem& p, const CostTable& cost, UmmaSpec* u)
     // 128-byte rows for K-major operands.)
     if (f64) BK = kc_ext <= 8 || double(ceil_div(kc_ext, 16) * 16) > 1.15 * double(ceil_div(kc_ext, 8) * 8) ? 8 : 16;
     else if (!a_kmajor && !b_kmajor) BK = kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32;
+    // A k chunk of 64 (eight MMAs per stage, stages of 64 KB per CTA of a pair): half the barrier round trips and
+    // half the copy instructions per flop.  The producer warp needs 700 to 900 cycles per stage for its
+    // wait / announce / copy sequence whatever the stage holds, which is more than the 512 cycles four MMAs take
+    // and less than the 1 024 of eight.  Only where it pads the chunked mode by at most a tenth more.
+    if (!f64 && bk_request == 64 && BK == 32 && kc_ext >= 64 &&
+        double(ceil_div(kc_ext, 64) * 64) <= 1.1 * double(ceil_div(kc_ext, 32) * 32))
+        BK = 64;
     u->BK = BK;
     std::vector<int> kdigits{kc};
     for (int id : p.K)
@@ -449,11 +516,20 @@ void plan_umma(const Problem& p, const CostTable& cost, UmmaSpec* u)
         // Measured on B200 the pair kernel does not beat one CTA per tile (GEMM 8192x8192x4096: 580 vs
         // 605 TFLOP/s; cfg5: 455 vs 526): the MMA of a pair reads half of B from the partner SM and issues
         // more slowly, which eats the saving in copies.  It therefore stays opt-in.
+        // With a k chunk of 64 the pair is the point: 64 KB per CTA per stage is what the 64 B/clk an SM takes in
+        // from L2 delivers in the 1 024 cycles the stage's eight MMAs need, where one CTA per 128 x 256 tile would
+        // need 96 KB.  Taken when there are at least two waves of pairs and four stages of k.
         bool pair = false;
         if (f64) b2 = u->b;
+        const bool can_pair = !f64 && u->tiles_m >= 2 && b2.slabs_per_tile % 2 == 0;
+        if (BK == 64) pair = can_pair && u->BN == 256 && ceil_div(u->tiles_m, 2) * tn2 >= 148 && u->k_iters >= 4;
         if (const char* e = std::getenv("TCONT_UMMA_PAIR")) {
             if (e[0] == '0') pair = false;
-            else if (e[0] == '1') pair = !f64 && u->tiles_m >= 2 && b2.slabs_per_tile % 2 == 0;
+            else if (e[0] == '1') pair = can_pair;
+        }
+        if (BK == 64 && !pair) {
+            u->why_not = "a k chunk of 64 is only used by CTA pairs";
+            return;
         }
         if (pair) {
             u->pair = true;
@@ -467,6 +543,11 @@ void plan_umma(const Problem& p, const CostTable& cost, UmmaSpec* u)
         const bool a_far = u->a.major == 1 && u->a.stride[u->a.kc_dim] * elt >= 65536;
         const bool b_far = u->b.major == 1 && u->b.stride[u->b.kc_dim] * elt >= 65536;
         u->far_fraction = ((a_far ? a_bytes : 0.0) + (b_far ? b_bytes : 0.0)) / (a_bytes + b_bytes);
+    }
+    if (!chunk_kmajor(&u->a, BK, u->a.slabs_per_tile) ||
+        !chunk_kmajor(&u->b, BK, u->pair ? u->b.slabs_per_tile / 2 : u->b.slabs_per_tile)) {
+        u->why_not = "a K-major operand cannot be staged with a k chunk of 64";
+        return;
     }
     if (!std::getenv("TCONT_UMMA_NO_MERGE")) {
         merge_slabs(&u->a, BK, u->a.slabs_per_tile);
@@ -487,7 +568,7 @@ void plan_umma(const Problem& p, const CostTable& cost, UmmaSpec* u)
     // wants a unit for each of its two consumer groups.
     {
         const int64_t tiles = (u->pair ? ceil_div(u->tiles_m, 2) : u->tiles_m) * u->tiles_n;
-        const int64_t wave = f64 ? 296 : 148;
+        const int64_t wave = f64 ? 296 : u->pair ? 74 : 148;
         const double flops = 2.0 * double(u->tiles_m * u->BM) * double(u->tiles_n * u->BN) * double(u->k_iters * u->BK);
         const double rate = (f64 ? cost.dmma_f64_tflops : cost.umma_tf32_tflops) * 1e6;  // flops per microsecond
         auto estimate = [&](int64_t s) {
@@ -513,7 +594,35 @@ void plan_umma(const Problem& p, const CostTable& cost, UmmaSpec* u)
     }
     u->raster_group = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(u->tiles_m,
                       std::llround(std::sqrt(148.0 * u->BN / u->BM)))));
+    // fused row modes: digit 0 carries no C stride of its own, the kernel splits the position (slab_elem_offset)
+    for (int which = 0; which < 2; ++which) {
+        UmmaOperand& o = which == 0 ? u->a : u->b;
+        if (split_inner[which] > 0) {
+            o.split_inner = split_inner[which];
+            o.split_outer_cstride = split_outer_cstride[which];
+            o.row_digit_cstride[0] = 0;
+        }
+    }
     u->eligible = true;
+}
+
+// The tcgen05 kernel is planned twice where that can pay: with a k chunk of 64 on CTA pairs, and, where that
+// form does not apply (short or ragged contracted mode, too few tiles, a B tile that does not split), with the
+// 32-wide chunk on one CTA per tile.  TCONT_UMMA_BK=32 and TCONT_UMMA_PAIR=0 keep the second form.
+void plan_umma(const Problem& p, const CostTable& cost, UmmaSpec* u)
+{
+    const char* bk = std::getenv("TCONT_UMMA_BK");
+    const char* pr = std::getenv("TCONT_UMMA_PAIR");
+    if (p.scalar_type != 1 && !(bk && std::atoi(bk) == 32) && !(pr && pr[0] == '0')) {
+        UmmaSpec v;
+        plan_umma_impl(p, cost, &v, 64);
+        if (v.eligible && v.BK == 64) {
+            *u = v;
+            return;
+        }
+    }
+    *u = UmmaSpec();
+    plan_umma_impl(p, cost, u, 32);
 }
 
 std::string perm_modes(const Problem& p, const std::vector<int>& ids)
@@ -749,6 +858,18 @@ int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* 
         if (!found) {  // no multiple of 32: keep the whole leading run together
             n = 1;
             while (n < rows.size() && find_char(pl.modeC, rows[n]) == find_char(pl.modeC, rows[n - 1]) + 1) ++n;
+        }
+        // FP64: a leading run too short for whole slabs (extent 6 or 12: a quarter of the rows empty) takes the
+        // next run of row modes along, so that the kernel's planner can stage both as one fused mode
+        // (operand-level row fusion in plan_umma)
+        if (scalar_type == 1 && n < rows.size()) {
+            int64_t lead_ext = 1;
+            for (size_t i = 0; i < n; ++i) lead_ext *= ext_of(rows[i]);
+            if (slab_padding_f64(lead_ext) > 1.08) {
+                size_t m = n + 1;
+                while (m < rows.size() && find_char(pl.modeC, rows[m]) == find_char(pl.modeC, rows[m - 1]) + 1) ++m;
+                n = m;
+            }
         }
         return std::make_pair(rows.substr(0, n), rows.substr(n));
     };

@@ -62,6 +62,7 @@ struct UmmaOperand {
     int slabs_per_tile = 4;
     int slabs_per_op = 1;    // consecutive slabs fetched by one TMA copy (merged boxes, MN-major only)
     int digit0_scale = 32;   // TMA coordinate of row digit 0 = chunk index * this
+    int k0_scale = 32;       // TMA coordinate of k digit 0 = k iteration * this (BK; BK / 32 for a K-major operand chunked in 32s)
     int oob_coord = 0;       // coordinate (in row digit 0's dim) that lies past the tensor: zero fill
     int n_row_digits = 1;  // slab index = mixed radix number; digit 0 = chunk of the slab mode
     int row_digit_dim[kMaxTmaRank] = {0};

@@ -145,6 +145,7 @@ __device__ __forceinline__ WorkUnit decode_unit(uint32_t unit, const UmmaParams&
     const uint32_t tile = splits > 1 ? unit / splits : unit;
     w.split = splits > 1 ? unit - tile * splits : 0u;
     decode_tile(tile, tiles_m, tiles_n, static_cast<uint32_t>(p.raster_group), &w.tm, &w.tn);
+    if (p.tn_rotate) w.tn = (w.tn + static_cast<uint32_t>(p.tn_rotate)) % tiles_n;
     w.it0 = static_cast<int>(w.split) * p.k_iters_per_split;
     w.n_it = p.k_iters - w.it0 < p.k_iters_per_split ? p.k_iters - w.it0 : p.k_iters_per_split;
     return w;

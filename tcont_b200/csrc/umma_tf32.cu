@@ -218,6 +218,9 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         uint32_t issued_mask = 0, issued_parity = 0;
         long long t_empty = 0;
         int cta_iter = 0;  // k iterations this CTA has gone through (test hook: one of them may be left out)
+        // One look at the next stage's empty barrier is issued right behind the copies of the current one, so
+        // that its latency overlaps theirs; `have_slot` says that look found the stage free.
+        bool have_slot = false;
 
         for (uint32_t tile = first_unit; tile < total_tiles; tile += unit_step) {
             const WorkUnit w = decode_unit(tile, p, tiles_m, tiles_n);
@@ -252,7 +255,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             int kd2 = w.it0 / (p.k_digit_ext[0] * p.k_digit_ext[1]);
             for (int it = 0; it < w.n_it; ++it, ++cta_iter) {
                 const long long t0 = p.prof ? clock64() : 0;
-                const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + stage), phase ^ 1u, abort_flag, 0, p.wait_limit_ns));
+                const bool ok = have_slot || __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + stage), phase ^ 1u, abort_flag, 0, p.wait_limit_ns));
                 if (p.prof) t_empty += clock64() - t0;
                 if (ok && cta_iter != p.test_skip_iter) {
                     // one arrival with the byte count of the whole stage; in a pair the MMA-issuing CTA
@@ -264,7 +267,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
 #pragma unroll
                         for (int t = 0; t < kMaxTmaRank; ++t) {
                             c[t] = base[t];
-                            if (o.k_digit_dim[0] == t) c[t] = kd0 * p.BK;
+                            if (o.k_digit_dim[0] == t) c[t] = kd0 * o.k0_scale;
                             if (o.k_digit_dim[1] == t) c[t] = kd1;
                             if (o.k_digit_dim[2] == t) c[t] = kd2;
                         }
@@ -286,6 +289,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                     stage = 0;
                     phase ^= 1u;
                 }
+                have_slot = __all_sync(0xffffffffu, mbar_test_wait(smem_u32(bar_empty + stage), phase ^ 1u));
             }
         }
         if (p.prof && lane == 0) p.prof[blockIdx.x * 8 + 3] = t_empty;
@@ -311,8 +315,10 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             const uint32_t b_lbo = p.b.major ? static_cast<uint32_t>(p.b.slab_bytes) : 16u;
             const uint32_t a_sbo = p.a.major ? 512u : 1024u, b_sbo = p.b.major ? 512u : 1024u;
             const uint32_t a_type = p.a.major ? 1u : 2u, b_type = p.b.major ? 1u : 2u;
-            const uint32_t a_kstep = p.a.major ? 1024u : 32u;
-            const uint32_t b_kstep = p.b.major ? 1024u : 32u;
+            // Byte offset of MMA k step kk inside an operand's part of the stage.  MN-major: 1 024 bytes per step
+            // (eight k rows of 128 bytes).  K-major: 32 bytes per step inside a 128-byte row of 32 k, and with a
+            // k chunk of 64 the second 32 k lie one whole slab image (slab rows x 128 bytes) further on.
+            const uint32_t a_chunk = static_cast<uint32_t>(p.a.slab_w) * 128u, b_chunk = static_cast<uint32_t>(p.b.slab_w) * 128u;
             const int ksteps = p.BK / 8;
             int stage = 0;
             uint32_t phase = 0;
@@ -336,8 +342,11 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                         const uint32_t a_base = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
                         const uint32_t b_base = a_base + a_tile_bytes;
                         for (int kk = 0; kk < ksteps; ++kk) {
-                            const uint64_t da = smem_desc(a_base + kk * a_kstep, a_lbo, a_sbo, a_type);
-                            const uint64_t db = smem_desc(b_base + kk * b_kstep, b_lbo, b_sbo, b_type);
+                            const uint32_t ukk = static_cast<uint32_t>(kk);
+                            const uint32_t a_off = p.a.major ? ukk * 1024u : (ukk >> 2) * a_chunk + (ukk & 3u) * 32u;
+                            const uint32_t b_off = p.b.major ? ukk * 1024u : (ukk >> 2) * b_chunk + (ukk & 3u) * 32u;
+                            const uint64_t da = smem_desc(a_base + a_off, a_lbo, a_sbo, a_type);
+                            const uint64_t db = smem_desc(b_base + b_off, b_lbo, b_sbo, b_type);
                             if (PAIR) umma_tf32_pair(tmem_c, da, db, idesc, (it | kk) != 0 ? 1u : 0u);
                             else umma_tf32(tmem_c, da, db, idesc, (it | kk) != 0 ? 1u : 0u);
                         }
@@ -427,7 +436,10 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             tcgen05_fence_after();
             if (ok) {
-                float* crow = p.C + static_cast<long long>(w.split) * p.split_stride + row_off;
+                // (with a contracted-mode split over several GPUs the tile's column range belongs to one owner, whose
+                // memory, local or a peer's over NVLink, takes the plain stores below)
+                float* cbase = p.owners > 1 ? p.owner_base[tn / static_cast<uint32_t>(p.tn_per_owner)] : p.C;
+                float* crow = cbase + static_cast<long long>(w.split) * p.split_stride + row_off;
                 const long long col_stride = p.b.row_elem_cstride;
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * p.BN);
                 const int nchunks = p.BN >> 5;

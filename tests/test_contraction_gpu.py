@@ -501,3 +501,26 @@ def test_bounded_wait_gives_up_cleanly(engine, oracle, monkeypatch):
     del broken
     out, desc = run_contraction(engine, c, A, B, 0)              # the same contraction on a fresh run
     check(oracle, c, A, B, out, desc)
+
+
+PAIR_K64_SHAPES = {
+    # CTA pairs on 256-wide tiles with a k chunk of 64 (forced here; the planner takes them on its own for large problems)
+    "kmajor_b_chunked": Contraction("abc", "adc", "db", dict(a=256, c=10, b=2048, d=128), F32),   # B K-major: two 32-wide chunks per copy
+    "k_tail_352": Contraction("abc", "adc", "db", dict(a=256, c=10, b=2048, d=352), F32),         # last stage half beyond the mode: zero fill
+    "both_kmajor": Contraction("ab", "ka", "kb", dict(a=2560, b=2048, k=192), F32),               # both operands chunked
+    "both_mn": Contraction("abcd", "aebf", "cfde", dict(a=128, b=8, c=128, d=40, e=4, f=64), F32),   # 64 k rows per slab, merged copies
+    "ragged_rows": Contraction("abc", "adc", "db", dict(a=200, c=13, b=2000, d=128), F32),        # partial slabs on both sides
+    "k_not_32": Contraction("ab", "ka", "kb", dict(a=2560, b=2048, k=100), F32),                  # K-major extent not a multiple of 32: stays on chunks of 32
+}
+
+
+@pytest.mark.parametrize("name", list(PAIR_K64_SHAPES))
+def test_cta_pairs_with_k_chunks_of_64(engine, oracle, monkeypatch, name):
+    monkeypatch.setenv("TCONT_UMMA_PAIR", "1")
+    c = PAIR_K64_SHAPES[name]
+    A, B = oracle.inputs(c, 61, -1.0, 1.0)
+    out, desc = run_contraction(engine, c, A, B, 1, launches=2)
+    u = desc["umma"]
+    assert desc["kernel"] == "umma_tf32" and u["pair"] is True and u["BN"] == 256, u
+    assert u["BK"] == (32 if name == "k_not_32" else 64), u
+    check(oracle, c, A, B, out, desc)

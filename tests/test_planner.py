@@ -45,7 +45,9 @@ def test_configs_pick_the_intended_kernels(engine):
     d2 = describe(engine, CONFIGS["cfg2"][0])
     assert d2["backend"] == "direct" and d2["kernel"] == "umma_tf32"
     u = d2["umma"]
-    assert (u["a_major"], u["b_major"], u["BN"], u["BK"], u["k_iters"]) == ("MN", "K", 256, 32, 32)
+    # CTA pairs on 256 x 256 tiles with a k chunk of 64: three stages of 64 KB per CTA, one copy per operand and stage
+    assert (u["a_major"], u["b_major"], u["BN"], u["BK"], u["k_iters"], u["pair"], u["stages"]) == ("MN", "K", 256, 64, 16, True, 3)
+    assert (u["a_slabs_per_copy"], u["b_slab_w"], u["b_slabs"]) == (4, 128, 2)
     assert u["tiles_m"] * u["tiles_n"] == 2048 and u["coalesced_store"] and u["smem_bytes"] <= 227 * 1024
     d4 = describe(engine, CONFIGS["cfg4"][0])
     assert d4["backend"] == "ttgt" and d4["kernel"] == "umma_tf32" and d4["umma"]["BK"] == 8
@@ -54,8 +56,8 @@ def test_configs_pick_the_intended_kernels(engine):
     # [a | f,e | b] so that every TMA box is one contiguous piece, and keeps B where it lies
     d5 = describe(engine, CONFIGS["cfg5"][0])
     assert d5["backend"] == "ttgt" and d5["transpose_a"] == [0, 3, 1, 2] and d5["transpose_b"] is None
-    assert d5["kernel"] == "umma_tf32" and d5["umma"]["k_iters"] == 512 and d5["umma"]["kc"] == "f"
-    assert d2["umma"]["pair"] is False and d2["umma"]["a_slabs_per_copy"] == 4
+    assert d5["kernel"] == "umma_tf32" and d5["umma"]["k_iters"] == 256 and d5["umma"]["kc"] == "f"
+    assert d5["umma"]["pair"] is True and d5["umma"]["BK"] == 64 and d5["umma"]["b_slabs_per_copy"] == 4
     d3 = describe(engine, CONFIGS["cfg3"][0])   # TMA-fed FP64 kernel: one 128-byte row of 16 doubles per box row
     assert d3["backend"] == "direct" and d3["kernel"] == "dmma_f64_tma"
     assert (d3["umma"]["BN"], d3["umma"]["BK"], d3["umma"]["stages"], d3["umma"]["k_iters"]) == (64, 16, 8, 3)
