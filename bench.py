@@ -152,6 +152,14 @@ class ClockSampler:
     def window(self, name, t0, t1):
         self.windows[name] = (t0, t1)
 
+    def reasons_between(self, t0, t1):
+        """Throttle reasons NVML reported between two host times (the samples taken so far)."""
+        out = set()
+        for r in list(self.samples):
+            if t0 <= r[0] <= t1:
+                out.update(name for bit, name in REASON_BITS.items() if r[5] & bit)
+        return sorted(out)
+
     def stop(self):
         self._stop.set()
         if self._thread is not None:
@@ -289,6 +297,28 @@ def parity_verdict(job, local_eq, A, B, out, kernel, seed):
     return v
 
 
+def contracted_parity(job, full_eq, A, B, mine, first, kernel, seed):
+    """Parity of a contracted-mode split: this rank's range of the SUMMED C (elements first .. first+len(mine) of the
+    whole tensor) against the oracle on the whole contraction, on sampled elements; same two verdicts as parity_verdict."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle_lib import F32, Contraction, Oracle
+    c = Contraction(full_eq.modeC, full_eq.modeA, full_eq.modeB, dict(full_eq.extent), int(full_eq.scalar_type))
+    oracle = Oracle()
+    oracle.set_num_threads(max(1, len(os.sched_getaffinity(0)) // job.world))
+    n = min(PARITY_SAMPLES // job.world, mine.size)
+    local = np.sort(np.random.default_rng(seed + 31 * job.rank).integers(0, mine.size, size=n))
+    idx = local + first
+    got = mine[local].astype(np.float64)
+    diff, nonfinite = oracle.compare(oracle.contract_sampled(c, A, B, idx, rounding=0), got, F32)
+    ref = oracle.contract_sampled(c, A, B, idx, rounding=1 if kernel == "umma_tf32" else 0)
+    scale = oracle.contract_sampled(c, np.abs(A), np.abs(B), idx, rounding=1)
+    worst = job.reduce(float((np.abs(got - ref) / (scale + 1e-30)).max()), "MAX")
+    diff_all, bad_all, n_all = job.reduce(float(diff), "SUM"), job.reduce(float(nonfinite), "SUM"), job.reduce(float(n), "SUM")
+    return {"samples": int(n_all), "outside_reference_criterion": int(diff_all), "fraction_outside": diff_all / max(n_all, 1.0),
+            "non_finite": int(bad_all), "worst_error_over_sum_abs_products": worst, "ranks_checked": job.world,
+            "pass": bool(bad_all == 0 and worst < 2e-5 and diff_all <= 0.005 * n_all)}
+
+
 def run_workload(job, args, name, scaling, split, split_mode, steps, warmup, tag, peaks, tf32_peak, e2e_steps, with_cpu):
     """One workload: shard, plan, prepare, warm up, time `steps` launches with CUDA events, then (untimed)
     single-launch spread, the end-to-end leg through the host-buffer entry point, the parity verdict and the
@@ -309,7 +339,10 @@ def run_workload(job, args, name, scaling, split, split_mode, steps, warmup, tag
     mC, mA, mB, st = w["C"], w["A"], w["B"], w["st"]
     sel = {"model": 0, "cogent": 1, "ttgt": 2}[args.backend]
     full_eq = tc.TCEquation(mC, mA, mB, dict(ext), "-", tc.ScalarType(st), tc.BackendSelection(sel))
-    contracted = split == "contracted"
+    if split.startswith("contracted") and world == 1:
+        split, split_mode = "external", None     # one GPU: nothing to sum across
+    contracted = split.startswith("contracted")
+    fused = contracted and split == "contracted"
     if contracted:
         scaling = "strong"
         shard_mode = split_mode or next(m for m in mA if m not in mC)
@@ -331,12 +364,16 @@ def run_workload(job, args, name, scaling, split, split_mode, steps, warmup, tag
     gA = global_eq.size(mA)
     a_cut, b_cut = shard_mode in mA, shard_mode in mB
 
+    whole = {}
+
     def operand(modes, n_local, n_global, cut, base):
         if not cut or world == 1:
             return tc.fill_uniform(n_local, local_eq.scalar_type, w["seed"], base, w["lo"], w["hi"])
         if scaling == "strong":
-            whole = tc.fill_uniform(n_global, local_eq.scalar_type, w["seed"], base, w["lo"], w["hi"])
-            return sharding.take_slice(whole, modes, global_eq.extent, shard_mode, sl)
+            full = tc.fill_uniform(n_global, local_eq.scalar_type, w["seed"], base, w["lo"], w["hi"])
+            if contracted:
+                whole[modes] = full      # the parity check of a contracted split needs the global operands
+            return sharding.take_slice(full, modes, global_eq.extent, shard_mode, sl)
         return tc.fill_uniform(n_local, local_eq.scalar_type, w["seed"], base + rank * n_local, w["lo"], w["hi"])
 
     A = operand(mA, nA, gA, a_cut, 0)
@@ -345,9 +382,25 @@ def run_workload(job, args, name, scaling, split, split_mode, steps, warmup, tag
     desc = plan.describe()
     nC = local_eq.size(mC)
     elt = 8 if st else 4
-    if contracted:
-        # partial C and the reduce-scatter output live in torch tensors; the engine works on them in
-        # place on torch's current stream, so the NCCL call is ordered behind the kernel
+    if fused:
+        # Contracted-mode split, fused: the kernel stores every partial tile straight into the owner's staging
+        # slots over NVLink (peer stores; the staging areas are exchanged as CUDA IPC handles), a one-element
+        # all-reduce on the same stream is the barrier among the ranks, then every owner adds its slots up.
+        dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+        reduced = torch.empty(nC // world, dtype=dA.dtype, device="cuda")
+        run = api.prepare_on_device(plan, dA.data_ptr(), dB.data_ptr(), reduced.data_ptr(), keep=(dA, dB, reduced))
+        run.set_stream(torch.cuda.current_stream().cuda_stream)
+        run.ksplit_enable(world, rank)
+        handles = [None] * world
+        dist.all_gather_object(handles, run.ksplit_export())
+        for r in range(world):
+            if r != rank:
+                run.ksplit_import(r, handles[r])
+        flag = torch.zeros(1, device="cuda")
+    elif contracted:
+        # the same split with the library collective: a full-size partial C per rank, then ncclReduceScatter
+        # (partial C and its output live in torch tensors; the engine works on them in place on torch's
+        # current stream, so the NCCL call is ordered behind the kernel)
         dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
         partial = torch.empty(nC, dtype=dA.dtype, device="cuda")
         reduced = torch.empty(nC // world, dtype=dA.dtype, device="cuda")
@@ -358,7 +411,10 @@ def run_workload(job, args, name, scaling, split, split_mode, steps, warmup, tag
 
     def step():
         tc.launch(run)
-        if contracted and world > 1:
+        if fused:
+            dist.all_reduce(flag)
+            run.ksplit_reduce()
+        elif contracted:
             dist.reduce_scatter_tensor(reduced, partial)
 
     for _ in range(warmup):
@@ -373,13 +429,15 @@ def run_workload(job, args, name, scaling, split, split_mode, steps, warmup, tag
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
-        launches = steps * (1 + int(desc["transpose_a"] is not None) + int(desc["transpose_b"] is not None))
+        launches = steps * (1 + int(desc["transpose_a"] is not None) + int(desc["transpose_b"] is not None) + int(fused))
     else:
         ms, launches = run.time_launches(steps)
     t_host1 = time.time()
     job.sync_all()
+    capped = False
     if job.sampler is not None:
         job.sampler.window(tag, t_host0, t_host1)
+        capped = "sw_power_cap" in job.sampler.reasons_between(t_host0, t_host1)
     ms_total = job.reduce(ms, "MAX")
     extra_steps = 0
     if tag == "headline" and ms_total < 300.0:
@@ -411,7 +469,14 @@ def run_workload(job, args, name, scaling, split, split_mode, steps, warmup, tag
     hA = torch.from_numpy(A).pin_memory()
     hB = torch.from_numpy(B).pin_memory()
     hC = torch.empty(nC, dtype=hA.dtype).pin_memory()
+    split_check = None
     if contracted:
+        # the summed result of the split, this rank's range of C, against the oracle on the WHOLE contraction
+        torch.cuda.synchronize()
+        if not args.no_parity:
+            split_check = contracted_parity(job, full_eq, whole.get(mA, A), whole.get(mB, B), reduced.cpu().numpy(), rank * (nC // world),
+                                            desc["kernel"], w["seed"])
+        del run
         run = tc.prepare(plan, A, B)   # the end-to-end leg measures the host-buffer entry point of one rank's share
     run.contract_host_ptr(hA.data_ptr(), hB.data_ptr(), hC.data_ptr())
     job.sync_all()
@@ -437,13 +502,14 @@ def run_workload(job, args, name, scaling, split, split_mode, steps, warmup, tag
         achieved = flops_local / (ms_step * 1e-3) / 1e12
         unit = "TFLOP/s"
         if st == 0:
-            # TF32 dense rate is half the bf16 rate of the same tensor cores: the driver-measured cuBLAS bf16
-            # figure, halved, is the denominator; the burst figure, whatever the clock record says, so that
-            # `frac` never moves with the denominator.  Beside it: the fraction of the sustained figure and of
-            # this process's own tcgen05 microbenchmark (resident zero operands, no loads: an upper bound no
-            # kernel that moves data reaches).
-            peak = peaks["bf16_tflops"] / 2.0
-            source = peaks["source"] + " burst bf16 dense / 2 (TF32 rate)"
+            # TF32 dense rate is half the bf16 rate of the same tensor cores, so the driver-measured cuBLAS bf16
+            # figures, halved, are the denominators: the sustained one for a timed region that ran on the power cap
+            # (NVML reported sw_power_cap inside it: seconds of back-to-back tensor work), the burst one otherwise.
+            # Both fractions are printed whichever `frac` uses, and beside them the fraction of this process's own
+            # tcgen05 microbenchmark (resident zero operands, no loads: an upper bound no kernel that moves data reaches).
+            peak = peaks["bf16_tflops_sustained" if capped else "bf16_tflops"] / 2.0
+            source = peaks["source"] + (" sustained (sw_power_cap seen in the timed region)" if capped else " burst") + " bf16 dense / 2 (TF32 rate)"
+            extra["frac_of_burst_bf16_half"] = achieved / (peaks["bf16_tflops"] / 2.0)
             extra["frac_of_sustained_bf16_half"] = achieved / (peaks["bf16_tflops_sustained"] / 2.0)
             if tf32_peak:
                 extra["tcgen05_tf32_peak_microbenchmark"] = tf32_peak
@@ -476,8 +542,12 @@ def run_workload(job, args, name, scaling, split, split_mode, steps, warmup, tag
     if extra_steps:
         rec["untimed_repeats_for_the_clock_record"] = extra_steps
     if contracted:
-        rec["config"]["collective"] = {"op": "ncclReduceScatter sum over NVLink, after every launch, inside the timed region",
-                                       "bytes_sent_per_gpu_per_step": int((world - 1) / world * nC * elt)}
+        rec["config"]["collective"] = {
+            "op": ("none: partial tiles stored straight into the owner's slots over NVLink by the contraction kernel (peer stores), "
+                   "one-element all-reduce as the barrier, owners add their slots; all inside the timed region") if fused
+            else "ncclReduceScatter sum over NVLink, after every launch, inside the timed region",
+            "nvlink_bytes_sent_per_gpu_per_step": int((world - 1) / world * nC * elt)}
+        rec["parity_of_the_summed_result"] = split_check
     if with_cpu:
         rec["cpu_baseline"], _ = cpu_baseline(name)
     return rec
@@ -501,9 +571,10 @@ def main():
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
                     help="strong (default): the named configuration is cut into N slices; weak: every rank runs the named "
                          "configuration and the global problem grows with N")
-    ap.add_argument("--split", default="external", choices=["external", "contracted"],
-                    help="contracted: cut a contracted mode; every rank produces a full-size partial C and an NCCL "
-                         "reduce-scatter over NVLink adds them (strong scaling only)")
+    ap.add_argument("--split", default="external", choices=["external", "contracted", "contracted-nccl"],
+                    help="contracted: cut a contracted mode; every rank's kernel stores its partial tiles straight into the "
+                         "owners' memory over NVLink and the owners add them up (strong scaling only); contracted-nccl: the "
+                         "same split with a full-size partial C per rank and ncclReduceScatter, for comparison")
     ap.add_argument("--split-mode", default=None, help="mode letter to cut (default: `a` for the sharded configurations, else the "
                                                        "slowest external mode; for --split contracted the first contracted mode of A)")
     args = ap.parse_args()
@@ -554,6 +625,8 @@ def main():
                 "roofline": head["roofline"], "parity": head["parity"]}
         if "cpu_baseline" in head:
             line["cpu_baseline"] = head["cpu_baseline"]
+        if "parity_of_the_summed_result" in head:
+            line["parity_of_the_summed_result"] = head["parity_of_the_summed_result"]
         if subs:
             line["configs"] = subs
         print(json.dumps(line), flush=True)

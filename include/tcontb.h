@@ -134,6 +134,35 @@ tcontb_status tcontb_run_contract_host(tcontb_run* run, const void* a_host, cons
  * inside a kernel gave up (the kernel then returns instead of hanging). */
 tcontb_status tcontb_run_device_status(tcontb_run* run, int* status);
 
+/* ---- contracted-mode split over the GPUs of one box ------------------------------------------
+ *
+ * No counterpart in the reference, which has no multi-GPU code.  The sharding that needs no exchange cuts an
+ * external mode (TCONT_NUM_GPUS / TCONT_SPLIT=ext:<mode>, or one run per process on a descriptor with the
+ * smaller extent).  Cutting a CONTRACTED mode instead gives every GPU a partial sum of the whole C; here the
+ * partial C never exists as a whole: C is cut into `ranks` contiguous ranges along its slowest mode, range o
+ * belongs to rank o, and the contraction kernel of rank r stores every finished tile of range o straight
+ * into rank o's memory (its own, or the peer's over NVLink: plain peer stores, no collective library, no
+ * remote loads).  After a barrier among the ranks each owner adds up its `ranks` slots.
+ *
+ * Per rank: create the run on the descriptor with the contracted extent divided by `ranks` (its slice of A
+ * and B); the run's C buffer receives only this rank's range (|C| / ranks elements).  Then
+ *   tcontb_run_ksplit_enable(run, ranks, rank)            allocates the staging area (2 * |C| elements)
+ *   tcontb_run_ksplit_export / _import                    one process per GPU: CUDA IPC handle of the staging
+ *                                                         area, sent to every other rank by the caller's own means
+ *   tcontb_run_ksplit_attach(run, peer_rank, peer_run)    the same between runs of one process
+ *   per step:  tcontb_run_launch(run);  <barrier among the ranks, ordered on the run's stream>;
+ *              tcontb_run_ksplit_reduce(run)
+ * Two sets of slots alternate between launches, so one barrier per step is enough.  Needs the tcgen05
+ * kernel without split-K, C's slowest mode in the operand that does not hold C's stride-1 mode, and an extent
+ * of that mode that cuts into whole tile columns per rank; otherwise TCONTB_UNSUPPORTED.
+ * Within one process TCONT_NUM_GPUS=<n> with TCONT_SPLIT=k:<mode> does all of this behind one run object. */
+tcontb_status tcontb_run_ksplit_enable(tcontb_run* run, int ranks, int rank);
+tcontb_status tcontb_run_ksplit_export(tcontb_run* run, void* handle, size_t handle_bytes);   /* 64 bytes */
+tcontb_status tcontb_run_ksplit_import(tcontb_run* run, int peer_rank, const void* handle, size_t handle_bytes);
+tcontb_status tcontb_run_ksplit_attach(tcontb_run* run, int peer_rank, tcontb_run* peer_run);
+tcontb_status tcontb_run_ksplit_reduce(tcontb_run* run);
+int64_t tcontb_run_ksplit_range_elements(const tcontb_run* run);
+
 /* ---- utilities ---------------------------------------------------------------------------- */
 
 /* Counter-based uniform fill (host): element i = lo + (hi-lo)*u_i, u_i = top 53 bits of

@@ -84,6 +84,13 @@ _lib.tcontb_run_time_launches.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_flo
 _lib.tcontb_run_contract_host.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64),
                                           C.POINTER(C.c_int64)]
 _lib.tcontb_run_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
+_lib.tcontb_run_ksplit_enable.argtypes = [C.c_void_p, C.c_int, C.c_int]
+_lib.tcontb_run_ksplit_export.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t]
+_lib.tcontb_run_ksplit_import.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.c_size_t]
+_lib.tcontb_run_ksplit_attach.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+_lib.tcontb_run_ksplit_reduce.argtypes = [C.c_void_p]
+_lib.tcontb_run_ksplit_range_elements.argtypes = [C.c_void_p]
+_lib.tcontb_run_ksplit_range_elements.restype = C.c_int64
 _lib.tcontb_fill_uniform.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_uint64, C.c_double, C.c_double]
 _lib.tcontb_transpose.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int), C.c_int,
                                   C.c_void_p]
@@ -180,6 +187,27 @@ class ExecutionRun:
         hi, ho = C.c_int64(), C.c_int64()
         _check(_lib.tcontb_run_contract_host(self._h, a_ptr, b_ptr, c_ptr, C.byref(hi), C.byref(ho)))
         return hi.value, ho.value
+
+    # ---- contracted-mode split over the GPUs of one box (include/tcontb.h) ----
+    def ksplit_enable(self, ranks: int, rank: int):
+        _check(_lib.tcontb_run_ksplit_enable(self._h, int(ranks), int(rank)))
+
+    def ksplit_export(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        _check(_lib.tcontb_run_ksplit_export(self._h, buf, 64))
+        return buf.raw
+
+    def ksplit_import(self, peer_rank: int, handle: bytes):
+        _check(_lib.tcontb_run_ksplit_import(self._h, int(peer_rank), handle, len(handle)))
+
+    def ksplit_attach(self, peer_rank: int, peer: "ExecutionRun"):
+        _check(_lib.tcontb_run_ksplit_attach(self._h, int(peer_rank), peer._h))
+
+    def ksplit_reduce(self):
+        _check(_lib.tcontb_run_ksplit_reduce(self._h))
+
+    def ksplit_range_elements(self) -> int:
+        return int(_lib.tcontb_run_ksplit_range_elements(self._h))
 
     def device_status(self) -> int:
         s = C.c_int()

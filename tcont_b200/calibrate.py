@@ -1,7 +1,11 @@
-"""Fills the planner's cost table from measurements on the current GPU and writes it as the
-"key value" file that TCONT_COST_TABLE names.
+"""Fills the planner's cost table from measurements on the current GPU and writes it as a "key value"
+file named after the device, beside the library, where the engine looks for it:
 
-    python -m tcont_b200.calibrate [-o cost_table.txt]
+    python -m tcont_b200.calibrate            # writes tcont_b200/tcont_cost_table.<device name>.txt
+    python -m tcont_b200.calibrate -o FILE    # any other place; use it with TCONT_COST_TABLE=FILE
+
+Lines whose key starts with `info_` are measurements for the record (rates of the helper kernels); the
+planner ignores them.
 
 The reference decides between its two backends with a LightGBM model trained offline on A100
 runs (final_model/*.json, src/backend_model_selector.cpp:365-403); the trainer is not part of its
@@ -104,19 +108,51 @@ def calibrate() -> dict:
     tc.warmup(run, 10)
     ms, _ = run.time_launches(200)
     table["launch_us"] = ms / 200 * 1e3
+
+    # ---- for the record: rates of the helper kernels (CUDA events; read + write bytes over time) ----
+    def permute_gbs(extent, perm, dtype, iters=10):
+        n = 1
+        for e in extent:
+            n *= e
+        x = torch.empty(n, device="cuda", dtype=dtype)
+        y = torch.empty_like(x)
+        for _ in range(3):
+            api.transpose(x.data_ptr(), y.data_ptr(), extent, perm, x.element_size(), stream)
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(iters):
+            api.transpose(x.data_ptr(), y.data_ptr(), extent, perm, x.element_size(), stream)
+        a1.record()
+        torch.cuda.synchronize()
+        return 2 * n * x.element_size() * iters / (a0.elapsed_time(a1) * 1e-3) / 1e9
+
+    # the input transpose of the large 4-D TF32 configuration: A[a,e,b,f] -> [a,f,e,b], rows of 128 floats kept
+    table["info_permute_rows_f32_gbs"] = permute_gbs([128, 128, 128, 128], [0, 3, 1, 2], torch.float32)
+    table["info_permute_rows_f64_gbs"] = permute_gbs([48, 48, 576, 16], [0, 2, 1, 3], torch.float64)
+    # a plain matrix transpose through the shared-memory tile
+    table["info_permute_tiled_f32_gbs"] = permute_gbs([8192, 8192], [1, 0], torch.float32)
+    table["info_permute_tiled_f64_gbs"] = permute_gbs([4096, 8192], [1, 0], torch.float64)
+    # split-K (contraction into four partial tensors + the kernel that adds them up), both precisions
+    lk = (("ab", "acd", "dbc"), dict(a=1024, b=1024, c=128, d=128))
+    table["info_splitk4_tf32_tflops"], _ = _rate(tc, api, torch, *lk, F32, env={"TCONT_SPLITK": "4"})
+    table["info_splitk4_f64_tflops"], _ = _rate(tc, api, torch, *lk, F64, env={"TCONT_SPLITK": "4"})
     return table
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("-o", "--output", default="tcont_cost_table.txt")
+    ap.add_argument("-o", "--output", default=None)
     args = ap.parse_args()
+    import torch
+    name = torch.cuda.get_device_name().replace(" ", "_").replace("/", "_")
+    out = args.output or os.path.join(os.path.dirname(os.path.abspath(__file__)), f"tcont_cost_table.{name}.txt")
+    os.environ["TCONT_COST_TABLE"] = os.devnull     # measure with the compiled-in defaults, not with an older table
     table = calibrate()
-    with open(args.output, "w") as f:
+    with open(out, "w") as f:
         for k, v in table.items():
             f.write(f"{k} {v:.6g}\n")
             print(f"{k} {v:.6g}")
-    print(f"wrote {args.output}; use it with TCONT_COST_TABLE={args.output}")
+    print(f"wrote {out}" + ("" if args.output is None else f"; use it with TCONT_COST_TABLE={out}"))
 
 
 if __name__ == "__main__":

@@ -2,12 +2,16 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <dlfcn.h>
+
 #include <cstdio>
 #include <cstdlib>
 #include <cmath>
 #include <cstring>
 #include <ctime>
+#include <map>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -44,6 +48,45 @@ inline uint64_t splitmix64(uint64_t z)
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
     z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
     return z ^ (z >> 31);
+}
+
+// The cost table plans are made with: the compiled-in defaults, overridden by the file TCONT_COST_TABLE names;
+// without that variable, by `tcont_cost_table.<device name>.txt` beside this library, where
+// `python -m tcont_b200.calibrate` writes what it measured on that kind of GPU (spaces in the name become '_').
+// The SM count always comes from the current device.  Without a usable device the plan is made for the
+// defaults (planning itself needs no GPU).  Cached per device.
+CostTable device_cost_table()
+{
+    static std::mutex mu;
+    static std::map<int, CostTable> cache;
+    int n = 0, dev = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0 || cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return load_cost_table();
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    const bool from_env = std::getenv("TCONT_COST_TABLE") != nullptr;
+    auto it = cache.find(dev);
+    if (it != cache.end() && !from_env) return it->second;
+    CostTable c = load_cost_table();
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) c.num_sms = sms;
+    if (from_env) return c;  // (not cached: tests and tools switch files through the environment)
+    cudaDeviceProp prop;
+    Dl_info info;
+    if (cudaGetDeviceProperties(&prop, dev) == cudaSuccess && dladdr(reinterpret_cast<const void*>(&device_cost_table), &info) && info.dli_fname) {
+        std::string name = prop.name, dir = info.dli_fname;
+        for (char& ch : name)
+            if (ch == ' ' || ch == '/') ch = '_';
+        const size_t slash = dir.rfind('/');
+        dir = slash == std::string::npos ? "." : dir.substr(0, slash);
+        read_cost_table_file(dir + "/tcont_cost_table." + name + ".txt", &c);
+        if (sms > 0) c.num_sms = sms;
+    } else {
+        cudaGetLastError();
+    }
+    cache[dev] = c;
+    return c;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -491,16 +534,28 @@ tcontb_status make_shards(tcontb_run* run, int gpus)
     TC_CUDA(cudaGetDeviceCount(&have));
     TC_CUDA(cudaGetDevice(&run->first_device));
     DeviceGuard guard(run->first_device, true);
-    if (run->first_device + gpus > have)
+    // Test mode: every shard on the first device (the slicing, routing, joining and gathering logic then runs on
+    // a box with one GPU; the shards' kernels run one after the other, none waits for another).
+    if (const char* od = std::getenv("TCONT_SHARDS_ON_ONE_DEVICE")) run->one_device = od[0] == '1';
+    if (!run->one_device && run->first_device + gpus > have)
         return fail(TCONTB_RUNTIME_ERROR, "TCONT_NUM_GPUS asks for more devices than the box has from the current device on");
     auto external = [&](char c) {
         return pl.modeC.find(c) != std::string::npos && ((pl.modeA.find(c) != std::string::npos) != (pl.modeB.find(c) != std::string::npos));
     };
     auto ext = [&](char c) { return pl.ext_val[pl.ext_mode.find(c)]; };
     char mode = 0;
-    if (const char* sp = std::getenv("TCONT_SPLIT")) {  // "ext:<mode>"
+    auto contracted = [&](char c) {
+        return pl.modeC.find(c) == std::string::npos && pl.modeA.find(c) != std::string::npos && pl.modeB.find(c) != std::string::npos;
+    };
+    const char* sp = std::getenv("TCONT_SPLIT");
+    if (sp && std::strncmp(sp, "k:", 2) == 0) {  // "k:<mode>": cut a contracted mode; partial tiles go straight to their owners
+        if (!sp[2] || !contracted(sp[2]) || ext(sp[2]) % gpus || gpus > kMaxOwners)
+            return fail(TCONTB_INVALID_ARGUMENT, "TCONT_SPLIT=k:<mode> must name a contracted mode whose extent divides over the GPUs (8 at most)");
+        mode = sp[2];
+        run->split_contracted = true;
+    } else if (sp) {  // "ext:<mode>"
         if (std::strncmp(sp, "ext:", 4) != 0 || !sp[4] || !external(sp[4]) || ext(sp[4]) % gpus)
-            return fail(TCONTB_INVALID_ARGUMENT, "TCONT_SPLIT must be ext:<mode> naming an external mode whose extent divides over the GPUs");
+            return fail(TCONTB_INVALID_ARGUMENT, "TCONT_SPLIT must be ext:<mode> naming an external mode, or k:<mode> naming a contracted one, whose extent divides over the GPUs");
         mode = sp[4];
     } else {
         // slowest mode of C first: its slices are contiguous blocks of C
@@ -519,14 +574,17 @@ tcontb_status make_shards(tcontb_run* run, int gpus)
         std::string err;
         const int rc = make_plan(pl.modeC.data(), static_cast<int>(pl.modeC.size()), pl.modeA.data(), static_cast<int>(pl.modeA.size()),
                                  pl.modeB.data(), static_cast<int>(pl.modeB.size()), pl.op, pl.scalar_type, pl.ext_mode.data(),
-                                 local_ext.data(), static_cast<int>(local_ext.size()), pl.backend_selection, load_cost_table(),
+                                 local_ext.data(), static_cast<int>(local_ext.size()), pl.backend_selection, device_cost_table(),
                                  &sh->plan, &err);
         if (rc) return fail(static_cast<tcontb_status>(rc), err);
         sh->elt = run->elt;
         const size_t bl = static_cast<size_t>(sh->plan.sizeL) * run->elt, br = static_cast<size_t>(sh->plan.sizeR) * run->elt;
         sh->hL.resize(bl);
         sh->hR.resize(br);
-        if (in_a) {
+        if (run->split_contracted) {  // both inputs carry the cut mode
+            slice_mode(run->hL.data(), sh->hL.data(), pl.modeA, pl, mode, g * len, len, run->elt, false);
+            slice_mode(run->hR.data(), sh->hR.data(), pl.modeB, pl, mode, g * len, len, run->elt, false);
+        } else if (in_a) {
             slice_mode(run->hL.data(), sh->hL.data(), pl.modeA, pl, mode, g * len, len, run->elt, false);
             sh->hR = run->hR;
         } else {
@@ -546,7 +604,30 @@ tcontb_status make_shards(tcontb_run* run, int gpus)
         cudaEvent_t ev = nullptr;
         TC_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
         run->shard_done.push_back(ev);
+        if (run->split_contracted) {
+            st = tcontb_run_ksplit_enable(sh.get(), gpus, g);
+            if (st != TCONTB_OK) return st;
+            cudaEvent_t ek = nullptr;
+            TC_CUDA(cudaEventCreateWithFlags(&ek, cudaEventDisableTiming));
+            run->shard_kernel.push_back(ek);
+        }
         run->shards.push_back(std::move(sh));
+    }
+    if (run->split_contracted) {
+        // every shard stores into every other shard's staging area: peer access both ways, then the pointers
+        for (int g = 0; g < gpus; ++g) {
+            TC_CUDA(cudaSetDevice(run->shard_device(static_cast<size_t>(g))));
+            for (int h = 0; h < gpus; ++h) {
+                if (h == g) continue;
+                if (!run->one_device) {
+                    const cudaError_t pe = cudaDeviceEnablePeerAccess(run->shard_device(static_cast<size_t>(h)), 0);
+                    if (pe == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+                    else if (pe != cudaSuccess) return fail(TCONTB_RUNTIME_ERROR, std::string("peer access between the GPUs of the split is not available: ") + cudaGetErrorString(pe));
+                }
+                const tcontb_status as = tcontb_run_ksplit_attach(run->shards[static_cast<size_t>(g)].get(), h, run->shards[static_cast<size_t>(h)].get());
+                if (as != TCONTB_OK) return as;
+            }
+        }
     }
     TC_CUDA(cudaSetDevice(run->first_device));
     run->kernels_per_launch = 0;
@@ -591,7 +672,7 @@ tcontb_status build_host_pipeline(tcontb_run* run)
         std::string err;
         const int rc = make_plan(pl.modeC.data(), static_cast<int>(pl.modeC.size()), pl.modeA.data(), static_cast<int>(pl.modeA.size()),
                                  pl.modeB.data(), static_cast<int>(pl.modeB.size()), pl.op, pl.scalar_type, pl.ext_mode.data(),
-                                 local_ext.data(), static_cast<int>(local_ext.size()), pl.backend_selection, load_cost_table(),
+                                 local_ext.data(), static_cast<int>(local_ext.size()), pl.backend_selection, device_cost_table(),
                                  &part->plan, &err);
         if (rc) return fail(static_cast<tcontb_status>(rc), err);
         part->elt = run->elt;
@@ -650,7 +731,7 @@ tcontb_status tcontb_plan_create(const tcontb_desc* d, tcontb_plan** out)
     std::unique_ptr<tcontb_plan> pl(new tcontb_plan());
     std::string err;
     const int rc = make_plan(d->modeC, d->nC, d->modeA, d->nA, d->modeB, d->nB, d->op, d->scalar_type, d->ext_mode, d->ext_val,
-                             d->n_ext, d->backend_selection, load_cost_table(), &pl->plan, &err);
+                             d->n_ext, d->backend_selection, device_cost_table(), &pl->plan, &err);
     if (rc) return fail(static_cast<tcontb_status>(rc), err);
     *out = pl.release();
     return TCONTB_OK;
@@ -803,14 +884,30 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
         DeviceGuard guard(run->first_device, true);
         // Every shard runs on its own device's NULL stream; the first device's NULL stream then waits
         // for all of them, so events the caller records there bracket the whole multi-GPU launch.
-        for (size_t g = 0; g < run->shards.size(); ++g) {
+        const size_t G = run->shards.size();
+        for (size_t g = 0; g < G; ++g) {
             TC_CUDA(cudaSetDevice(run->shard_device(g)));
+            if (run->split_contracted)  // the sums of the previous launch read what this launch's peers are about to overwrite two launches on
+                for (size_t h = 0; h < G; ++h)
+                    if (h != g) TC_CUDA(cudaStreamWaitEvent(nullptr, run->shard_done[h], 0));
             const tcontb_status st = tcontb_run_launch(run->shards[g].get());
             if (st != TCONTB_OK) {
                 cudaSetDevice(run->first_device);
                 return st;
             }
-            TC_CUDA(cudaEventRecord(run->shard_done[g], nullptr));
+            if (run->split_contracted) TC_CUDA(cudaEventRecord(run->shard_kernel[g], nullptr));
+            else TC_CUDA(cudaEventRecord(run->shard_done[g], nullptr));
+        }
+        if (run->split_contracted) {
+            // every shard's kernel has stored its partial tiles into the owners' slots: each owner adds its slots up
+            for (size_t g = 0; g < G; ++g) {
+                TC_CUDA(cudaSetDevice(run->shard_device(g)));
+                for (size_t h = 0; h < G; ++h)
+                    if (h != g) TC_CUDA(cudaStreamWaitEvent(nullptr, run->shard_kernel[h], 0));
+                const tcontb_status st = tcontb_run_ksplit_reduce(run->shards[g].get());
+                if (st != TCONTB_OK) return st;
+                TC_CUDA(cudaEventRecord(run->shard_done[g], nullptr));
+            }
         }
         TC_CUDA(cudaSetDevice(run->first_device));
         for (size_t g = 1; g < run->shards.size(); ++g) TC_CUDA(cudaStreamWaitEvent(nullptr, run->shard_done[g], 0));
@@ -842,8 +939,24 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
             q.C = static_cast<float*>(run->splitk.ptr) + static_cast<long long>(pass) * pl.umma.k_splits * pl.sizeC;
             TC_CUDA(launch_umma_tf32(q, maps[pass][0], maps[pass][1], pl.umma.smem_bytes, run->num_sms, run->stream));
         }
-    } else if (pl.kernel == KERNEL_UMMA_TF32)
+    } else if (pl.kernel == KERNEL_UMMA_TF32) {
+        if (run->ks.world > 1) {
+            // contracted-mode split: tile columns of range o go to slot [set][rank] of owner o's staging area
+            auto& ks = run->ks;
+            if (scaled) return fail(TCONTB_UNSUPPORTED, "alpha and beta are not available with a contracted-mode split");
+            umma.owners = ks.world;
+            umma.tn_per_owner = static_cast<int>(pl.umma.tiles_n / ks.world);
+            umma.tn_rotate = ((ks.rank + 1) % ks.world) * umma.tn_per_owner;
+            for (int o = 0; o < ks.world; ++o) {
+                if (!ks.peer[o]) return fail(TCONTB_INVALID_ARGUMENT, "contracted-mode split: the staging area of rank " + std::to_string(o) + " was never attached");
+                umma.owner_base[o] = static_cast<float*>(ks.peer[o]) + (static_cast<int64_t>(ks.set) * ks.world + ks.rank) * ks.chunk -
+                                     static_cast<int64_t>(o) * ks.chunk;
+            }
+            ks.last_set = ks.set;
+            ks.set ^= 1;
+        }
         TC_CUDA(launch_umma_tf32(umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
+    }
     else if (pl.kernel == KERNEL_DMMA_F64_TMA)
         TC_CUDA(launch_dmma_tma(umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
     else if (pl.kernel == KERNEL_DMMA_F64)
@@ -938,6 +1051,16 @@ tcontb_status tcontb_run_copy_output(tcontb_run* run, void* dst, size_t bytes)
         if (bytes != have) return fail(TCONTB_INVALID_ARGUMENT, "A multi-GPU run copies the whole output tensor or nothing");
         DeviceGuard guard(run->first_device, true);
         const Plan& pl = run->plan;
+        if (run->split_contracted) {
+            // shard g owns the g-th contiguous range of C (cut along C's slowest mode) and holds it at the start of its C buffer
+            const size_t chunk_bytes = have / run->shards.size();
+            for (size_t g = 0; g < run->shards.size(); ++g) {
+                TC_CUDA(cudaSetDevice(run->shard_device(g)));
+                TC_CUDA(cudaMemcpy(static_cast<unsigned char*>(dst) + g * chunk_bytes, run->shards[g]->dC, chunk_bytes, cudaMemcpyDeviceToHost));
+            }
+            TC_CUDA(cudaSetDevice(run->first_device));
+            return fail_if_device_gave_up(run);
+        }
         const int64_t len = pl.ext_val[pl.ext_mode.find(run->split_mode)] / static_cast<int64_t>(run->shards.size());
         std::vector<unsigned char> part;
         for (size_t g = 0; g < run->shards.size(); ++g) {
@@ -1060,6 +1183,88 @@ tcontb_status tcontb_run_device_status(tcontb_run* run, int* status)
         if (st != TCONTB_OK) return st;
         if (s1 > *status) *status = s1;
     }
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_ksplit_enable(tcontb_run* run, int world, int rank)
+{
+    if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    TC_NOT_SHARDED(run, "tcontb_run_ksplit_enable");
+    if (world < 2 || world > kMaxOwners || rank < 0 || rank >= world) return fail(TCONTB_INVALID_ARGUMENT, "contracted-mode split: need 2..8 ranks and 0 <= rank < ranks");
+    if (run->ks.world) return fail(TCONTB_INVALID_ARGUMENT, "contracted-mode split is already enabled on this run");
+    const Plan& pl = run->plan;
+    const Problem& p = pl.prob;
+    const UmmaSpec& u = pl.umma;
+    if (pl.kernel != KERNEL_UMMA_TF32 || u.k_splits != 1 || run->tf32x3)
+        return fail(TCONTB_UNSUPPORTED, "contracted-mode split needs the tcgen05 kernel without split-K (Float32 operands TMA can stage; TCONT_SPLITK=1)");
+    // C's slowest mode must be a column mode of the kernel (role B), the most significant digit of the column
+    // slab index, and its ranges must fall on tile-column boundaries: a tile then has exactly one owner.
+    if (p.C.empty() || p.N.empty() || p.C.back() != p.N.back())
+        return fail(TCONTB_UNSUPPORTED, "contracted-mode split: C's slowest mode must belong to the operand that does not hold C's stride-1 mode");
+    const Mode& slow = p.modes[static_cast<size_t>(p.C.back())];
+    const int64_t sb = u.b.slabs_per_tile;
+    const bool single = p.N.size() == 1;
+    if (slow.extent % world || u.b.total_slabs % world || (u.b.total_slabs / world) % sb || u.tiles_n % world || pl.sizeC % world ||
+        (single && (slow.extent / world) % u.b.slab_w))
+        return fail(TCONTB_UNSUPPORTED, "contracted-mode split: the extent of C's slowest mode does not cut into whole tile columns per rank");
+    auto& ks = run->ks;
+    ks.chunk = pl.sizeC / world;
+    if ((static_cast<size_t>(ks.chunk) * run->elt) % 16) return fail(TCONTB_UNSUPPORTED, "contracted-mode split: a rank's range of C is not a multiple of 16 bytes");
+    TC_CUDA(ks.staging.alloc(static_cast<size_t>(2) * world * static_cast<size_t>(ks.chunk) * run->elt));
+    ks.world = world;
+    ks.rank = rank;
+    ks.peer[rank] = ks.staging.ptr;
+    return TCONTB_OK;
+}
+
+int64_t tcontb_run_ksplit_range_elements(const tcontb_run* run) { return run ? run->ks.chunk : 0; }
+
+tcontb_status tcontb_run_ksplit_export(tcontb_run* run, void* handle, size_t handle_bytes)
+{
+    if (!run || !handle) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun or handle buffer is empty");
+    if (!run->ks.world) return fail(TCONTB_INVALID_ARGUMENT, "contracted-mode split is not enabled on this run");
+    if (handle_bytes < sizeof(cudaIpcMemHandle_t)) return fail(TCONTB_INVALID_ARGUMENT, "handle buffer is smaller than a CUDA IPC memory handle (64 bytes)");
+    cudaIpcMemHandle_t h;
+    TC_CUDA(cudaIpcGetMemHandle(&h, run->ks.staging.ptr));
+    std::memcpy(handle, &h, sizeof(h));
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_ksplit_import(tcontb_run* run, int peer_rank, const void* handle, size_t handle_bytes)
+{
+    if (!run || !handle) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun or handle is empty");
+    auto& ks = run->ks;
+    if (!ks.world || peer_rank < 0 || peer_rank >= ks.world || peer_rank == ks.rank) return fail(TCONTB_INVALID_ARGUMENT, "contracted-mode split: bad peer rank");
+    if (handle_bytes < sizeof(cudaIpcMemHandle_t)) return fail(TCONTB_INVALID_ARGUMENT, "handle is smaller than a CUDA IPC memory handle (64 bytes)");
+    if (ks.peer[peer_rank]) return fail(TCONTB_INVALID_ARGUMENT, "contracted-mode split: this peer is already attached");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    TC_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    ks.peer[peer_rank] = p;
+    ks.opened[peer_rank] = true;
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_ksplit_attach(tcontb_run* run, int peer_rank, tcontb_run* peer)
+{
+    if (!run || !peer) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    auto& ks = run->ks;
+    if (!ks.world || peer_rank < 0 || peer_rank >= ks.world || peer_rank == ks.rank || peer->ks.world != ks.world || peer->ks.rank != peer_rank ||
+        peer->ks.chunk != ks.chunk)
+        return fail(TCONTB_INVALID_ARGUMENT, "contracted-mode split: the peer run is not rank " + std::to_string(peer_rank) + " of the same split");
+    ks.peer[peer_rank] = peer->ks.staging.ptr;
+    return TCONTB_OK;
+}
+
+tcontb_status tcontb_run_ksplit_reduce(tcontb_run* run)
+{
+    if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
+    auto& ks = run->ks;
+    if (!ks.world) return fail(TCONTB_INVALID_ARGUMENT, "contracted-mode split is not enabled on this run");
+    const unsigned char* slots = static_cast<const unsigned char*>(ks.staging.ptr) +
+                                 static_cast<size_t>(ks.last_set) * ks.world * static_cast<size_t>(ks.chunk) * run->elt;
+    TC_CUDA(launch_splitk_reduce(slots, run->dC, ks.chunk, ks.world, ks.chunk, static_cast<int>(run->elt), run->stream, 1.0, 0.0));
     return TCONTB_OK;
 }
 

@@ -491,7 +491,7 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
             finish_operand(p, p.B, p.N, cand, BK, kdigits, &tmp);
             if (tmp.slabs_per_tile < 1) break;
             bn = cand;
-            if (u->tiles_m * ceil_div(tmp.total_slabs, tmp.slabs_per_tile) >= 148) break;
+            if (u->tiles_m * ceil_div(tmp.total_slabs, tmp.slabs_per_tile) >= cost.num_sms) break;
         }
     }
     u->BN = bn;
@@ -522,7 +522,7 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
         bool pair = false;
         if (f64) b2 = u->b;
         const bool can_pair = !f64 && u->tiles_m >= 2 && b2.slabs_per_tile % 2 == 0;
-        if (BK == 64) pair = can_pair && u->BN == 256 && ceil_div(u->tiles_m, 2) * tn2 >= 148 && u->k_iters >= 4;
+        if (BK == 64) pair = can_pair && u->BN == 256 && ceil_div(u->tiles_m, 2) * tn2 >= cost.num_sms && u->k_iters >= 4;
         if (const char* e = std::getenv("TCONT_UMMA_PAIR")) {
             if (e[0] == '0') pair = false;
             else if (e[0] == '1') pair = can_pair;
@@ -564,11 +564,11 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
     // computed as separate work units (partials summed by a second kernel).  Of the admissible counts
     // (ranges of at least 4 iterations, workspace of at most 512 MB) the one with the smallest estimate
     // wins: arithmetic over the share of the last wave's SMs that have a unit, plus the partials written
-    // and read back.  A wave is 148 units for the tcgen05 kernel and 296 for the FP64 kernel, which
+    // and read back.  A wave is one unit per SM for the tcgen05 kernel (per SM pair for CTA pairs) and two for the FP64 kernel, which
     // wants a unit for each of its two consumer groups.
     {
         const int64_t tiles = (u->pair ? ceil_div(u->tiles_m, 2) : u->tiles_m) * u->tiles_n;
-        const int64_t wave = f64 ? 296 : u->pair ? 74 : 148;
+        const int64_t wave = f64 ? 2 * cost.num_sms : u->pair ? cost.num_sms / 2 : cost.num_sms;
         const double flops = 2.0 * double(u->tiles_m * u->BM) * double(u->tiles_n * u->BN) * double(u->k_iters * u->BK);
         const double rate = (f64 ? cost.dmma_f64_tflops : cost.umma_tf32_tflops) * 1e6;  // flops per microsecond
         auto estimate = [&](int64_t s) {
@@ -593,7 +593,7 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
         u->k_splits = static_cast<int>(ceil_div(u->k_iters, u->k_iters_per_split));
     }
     u->raster_group = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(u->tiles_m,
-                      std::llround(std::sqrt(148.0 * u->BN / u->BM)))));
+                      std::llround(std::sqrt(double(cost.num_sms) * u->BN / u->BM)))));
     // fused row modes: digit 0 carries no C stride of its own, the kernel splits the position (slab_elem_offset)
     for (int which = 0; which < 2; ++which) {
         UmmaOperand& o = which == 0 ? u->a : u->b;
@@ -645,11 +645,11 @@ void fill_transpose(const std::string& src, const std::string& dst, const std::s
     }
 }
 
-// Share of the last wave's SMs that have a tile: t tiles on 148 SMs take ceil(t / 148) rounds.
-double wave_efficiency(int64_t tiles)
+// Share of the last wave's SMs that have a tile: t tiles on n SMs take ceil(t / n) rounds.
+double wave_efficiency(int64_t tiles, int sms)
 {
     const int64_t t = std::max<int64_t>(tiles, 1);
-    return double(t) / double(ceil_div(t, 148) * 148);
+    return double(t) / double(ceil_div(t, sms) * sms);
 }
 
 // The gather kernel fetches 16 bytes per load when the stride-1 mode of an operand is the first row
@@ -677,7 +677,7 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
         return double(ceil_div(p.Mtot, bm) * bm) / double(p.Mtot) * double(ceil_div(p.Ntot, bn) * bn) / double(p.Ntot);
     };
     if (kernel == KERNEL_SIMT && p.scalar_type == 1)
-        rate *= wave_efficiency(ceil_div(p.Mtot, 64) * ceil_div(p.Ntot, 64)) / padded(64, 64);
+        rate *= wave_efficiency(ceil_div(p.Mtot, 64) * ceil_div(p.Ntot, 64), c.num_sms) / padded(64, 64);
     // TMA-fed kernels: slabs and k chunks are whole, ragged extents are zero-filled and multiplied anyway
     // (extents of 72 in 32-wide slabs and chunks: abcd-aefb-fdce ran at 138 TFLOP/s direct, 415 after a
     // transpose that fuses the ragged modes away)
@@ -688,7 +688,7 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
         extra_us += c.launch_us + 2.0 * double(u.k_splits) * double(p.sizeC) * elt / (c.hbm_gbs * 1e3);
     }
     if (kernel == KERNEL_DMMA_F64_TMA) {
-        rate = c.dmma_f64_tflops * wave_efficiency(u.tiles_m * u.tiles_n * u.k_splits) / tma_padding;
+        rate = c.dmma_f64_tflops * wave_efficiency(u.tiles_m * u.tiles_n * u.k_splits, c.num_sms) / tma_padding;
         // Rows of a slab that are not contiguous in C are stored element by element
         // (abcdef-dega-gfbc: 37.7 M elements of C, 1.08 ms against 0.10 ms for its coalesced siblings).
         // (runs shorter than 64 bytes count as scattered too: cfg3 cut to a = 6 ran at 17.6 TFLOP/s here
@@ -702,11 +702,11 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
         const double r = p.Ntot <= 48 ? c.dmma_f64_gather_narrow_tflops
                                       : (gathers_16_bytes(p) ? c.dmma_f64_gather_tflops : c.dmma_f64_gather8_tflops);
         rate = r *
-               wave_efficiency(ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn)) / padded(bm, bn);
+               wave_efficiency(ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn), c.num_sms) / padded(bm, bn);
     }
     if (kernel == KERNEL_UMMA_TF32) {
         rate = c.umma_tf32_tflops * (1.0 - c.far_row_penalty * u.far_fraction) *
-               wave_efficiency((u.pair ? ceil_div(u.tiles_m, 2) : u.tiles_m) * u.tiles_n * u.k_splits) / tma_padding;
+               wave_efficiency((u.pair ? ceil_div(u.tiles_m, 2) : u.tiles_m) * u.tiles_n * u.k_splits, u.pair ? c.num_sms / 2 : c.num_sms) / tma_padding;
         // Rows of a slab that are not contiguous in C are stored element by element, a 32-byte sector each
         // (abcd-dbea-ec, 9.0 M elements of C: 0.125 ms against a 0.022 ms traffic floor).
         if (u.a.row_elem_cstride != 1) scatter_us = double(p.sizeC) * double(u.k_splits) * c.scatter_store_f32_ps * 1e-6;
@@ -730,8 +730,8 @@ int pick_kernel(const Problem& p, const UmmaSpec& u, const CostTable& c)
     int best = KERNEL_SIMT;
     double best_us = contraction_us(p, KERNEL_SIMT, u, c);
     const int64_t bn = p.Ntot <= 48 ? 32 : 64, bm = p.Ntot <= 48 ? 256 : 128;  // the gather kernel's smallest fitting tile
-    if (k && std::strcmp(k, "gather") == 0 && ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn) >= 148) return KERNEL_DMMA_F64;
-    if (ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn) >= 148) {
+    if (k && std::strcmp(k, "gather") == 0 && ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn) >= c.num_sms) return KERNEL_DMMA_F64;
+    if (ceil_div(p.Mtot, bm) * ceil_div(p.Ntot, bn) >= c.num_sms) {
         const double us = contraction_us(p, KERNEL_DMMA_F64, u, c);
         if (us < best_us) best = KERNEL_DMMA_F64, best_us = us;
     }
@@ -746,12 +746,11 @@ int pick_kernel(const Problem& p, const UmmaSpec& u, const CostTable& c)
 
 }  // namespace
 
-CostTable load_cost_table()
+bool read_cost_table_file(const std::string& path, CostTable* table)
 {
-    CostTable c;
-    const char* path = std::getenv("TCONT_COST_TABLE");
-    if (!path) return c;
+    CostTable& c = *table;
     std::ifstream f(path);
+    if (!f) return false;
     std::string key;
     double v;
     // "key value" pairs, one per line; unknown keys are ignored.
@@ -768,7 +767,15 @@ CostTable load_cost_table()
         else if (key == "scatter_store_ps") c.scatter_store_ps = v;
         else if (key == "scatter_store_f32_ps") c.scatter_store_f32_ps = v;
         else if (key == "far_row_penalty") c.far_row_penalty = v;
+        else if (key == "num_sms" && v >= 1) c.num_sms = static_cast<int>(v);
     }
+    return true;
+}
+
+CostTable load_cost_table()
+{
+    CostTable c;
+    if (const char* path = std::getenv("TCONT_COST_TABLE")) read_cost_table_file(path, &c);
     return c;
 }
 

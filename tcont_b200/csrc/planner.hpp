@@ -118,6 +118,7 @@ struct CostTable {
     double scatter_store_ps = 28.0;         // per element of C stored on its own (TMA-fed FP64 kernel)
     double scatter_store_f32_ps = 11.0;     // the same for the tcgen05 kernel's 4-byte elements
     double launch_us = 3.0;
+    int num_sms = 148;  // SMs of the device the plan is made for (api.cpp fills it in from the current device)
     // Fraction of the tcgen05 rate lost per unit of staged bytes whose K rows lie 64 KB or more apart
     // (cfg5 on B200: 274 / 434 / 605 TFLOP/s with two thirds / one third / none of the bytes far-strided).
     double far_row_penalty = 0.85;
@@ -148,7 +149,10 @@ int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* 
               Plan* plan, std::string* err);
 
 std::string describe_plan(const Plan& plan);
+// Defaults, overridden by the "key value" file TCONT_COST_TABLE names, if any.
 CostTable load_cost_table();
+// Reads "key value" lines into `table` (unknown keys are ignored); false when the file cannot be opened.
+bool read_cost_table_file(const std::string& path, CostTable* table);
 
 // Offset tables of the GEMM view: address(A, m, k) = offAm[m] + offAk[k] and so on.
 struct OffsetTables {

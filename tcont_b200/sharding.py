@@ -69,3 +69,21 @@ def shard_contracted(eq, mode: str, world: int, rank: int):
     ext = dict(eq.extent)
     ext[mode] = local
     return replace(eq, extent=ext), slice(rank * local, (rank + 1) * local)
+
+
+def owner_range(n_elements: int, world: int, owner: int) -> slice:
+    """Contracted-mode split: C is cut into `world` contiguous ranges along its slowest mode and range o
+    belongs to rank o (tcontb_run_ksplit_* in include/tcontb.h).  The range as a slice of the flat tensor."""
+    if n_elements % world:
+        raise ValueError(f"{n_elements} elements of C do not cut into {world} equal ranges")
+    n = n_elements // world
+    return slice(owner * n, (owner + 1) * n)
+
+
+def sum_owner_slots(slots) -> np.ndarray:
+    """What an owner does with the `world` partial ranges stored into its slots: add them in rank order
+    (the order is fixed, so the result does not depend on which peer's stores arrived first)."""
+    out = np.array(slots[0], dtype=slots[0].dtype, copy=True)
+    for part in slots[1:]:
+        out += part
+    return out

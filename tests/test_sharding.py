@@ -73,6 +73,52 @@ def _worker_ksplit(rank, world, port, result_path):
     dist.destroy_process_group()
 
 
+def _worker_owner_slots(rank, world, port, result_path):
+    """The protocol of the fused contracted split: rank r sends range o of its partial C to owner o (the GPU
+    kernel stores it there tile by tile), every owner adds its `world` slots in rank order, and the owners'
+    ranges laid end to end are C."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="2")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle_lib import F64, Contraction, Oracle
+    from tcont_b200 import TCEquation, ScalarType, sharding
+    oracle = Oracle()
+    eq = TCEquation("abcd", "aebf", "cfde", dict(a=8, b=6, c=4, d=6, e=4, f=3), "-", ScalarType.Float64)
+    cfull = Contraction(eq.modeC, eq.modeA, eq.modeB, dict(eq.extent), F64)
+    A, B = oracle.inputs(cfull, 6)
+    local, sl = sharding.shard_contracted(eq, "e", world, rank)
+    a_loc = sharding.take_slice(A, eq.modeA, eq.extent, "e", sl)
+    b_loc = sharding.take_slice(B, eq.modeB, eq.extent, "e", sl)
+    partial = oracle.contract(Contraction(local.modeC, local.modeA, local.modeB, dict(local.extent), F64), a_loc, b_loc)
+    n = partial.size
+    slots = [None] * world
+    slots[rank] = partial[sharding.owner_range(n, world, rank)].copy()
+    sends = []
+    for o in range(world):
+        if o != rank:
+            sends.append(dist.isend(torch.from_numpy(partial[sharding.owner_range(n, world, o)].copy()), dst=o))
+    for src in range(world):
+        if src != rank:
+            buf = torch.empty(n // world, dtype=torch.float64)
+            dist.recv(buf, src=src)
+            slots[src] = buf.numpy()
+    for w in sends:
+        w.wait()
+    mine = torch.from_numpy(sharding.sum_owner_slots(slots))
+    chunks = [torch.empty(n // world, dtype=torch.float64) for _ in range(world)]
+    dist.all_gather(chunks, mine)
+    if rank == 0:
+        np.save(result_path, np.stack([torch.cat(chunks).numpy(), oracle.contract(cfull, A, B)]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_owner_slot_protocol_sums_to_unsharded(tmp_path, engine):
+    path = str(tmp_path / "out.npy")
+    mp.spawn(_worker_owner_slots, args=(2, _free_port(), path), nprocs=2, join=True)
+    got, want = np.load(path)
+    np.testing.assert_allclose(got, want, rtol=1e-13, atol=1e-13)   # the order of the partial sums differs
+
+
 def test_contracted_split_sums_to_unsharded(tmp_path, engine):
     path = str(tmp_path / "out.npy")
     mp.spawn(_worker_ksplit, args=(2, _free_port(), path), nprocs=2, join=True)
