@@ -86,28 +86,33 @@ def calibrate() -> dict:
     # scattered stores of the TMA-fed kernels: two contractions of the same size with a short contracted
     # extent, one whose tile rows run along C's stride-1 mode and one whose rows do not (every element of C
     # stored on its own); the time of the second per element of C
-    ext6 = dict(a=24, b=16, c=16, d=24, e=16, f=16, g=24)
-    size_c = 24 * 16 * 16 * 24 * 16 * 16
+    # (a = 30: no multiple of 8, so the FP64 kernel cannot store across slabs and the rows really are scattered)
+    ext6 = dict(a=30, b=16, c=16, d=24, e=16, f=16, g=24)
+    size_c = 30 * 16 * 16 * 24 * 16 * 16
     flops6 = 2.0 * size_c * 24
     for key, scalar in (("scatter_store_ps", F64), ("scatter_store_f32_ps", F32)):
         _, k1 = _rate(tc, api, torch, ("abcdef", "degb", "gfac"), ext6, scalar)
         t_scat, k2 = _rate(tc, api, torch, ("abcdef", "dega", "gfbc"), ext6, scalar)
         if k1 == k2 and k1 in ("dmma_f64_tma", "umma_tf32"):
             table[key] = flops6 / (t_scat * 1e12) / size_c * 1e12
-    # far-row penalty: the same 4-D contraction with the chunked contracted mode near (f) and far (e) in B
-    shape = (("abcd", "aebf", "cfde"), dict(a=128, b=128, c=128, d=128, e=64, f=64))
-    near, _ = _rate(tc, api, torch, *shape, F32, iters=3, env={"TCONT_UMMA_KC": "f"})
-    far, _ = _rate(tc, api, torch, *shape, F32, iters=3, env={"TCONT_UMMA_KC": "e"})
-    # kc=f: A's rows are far (1/3 of a stage's bytes); kc=e: B's rows are far (2/3): rate ~ 1 - p * share
-    table["far_row_penalty"] = max(0.0, min(1.0, (near - far) / max(near * (2 / 3) - far * (1 / 3), 1e-9)))
-    # launch overhead: a contraction too small to matter
-    eq = tc.TCEquation("ab", "ak", "kb", dict(a=64, b=64, k=8), "-", F64, tc.BackendSelection.COGENT)
-    a = torch.zeros(512, device="cuda", dtype=torch.float64)
-    c = torch.zeros(4096, device="cuda", dtype=torch.float64)
-    run = api.prepare_on_device(tc.plan(eq), a.data_ptr(), a.data_ptr(), c.data_ptr(), keep=(a, c))
-    tc.warmup(run, 10)
-    ms, _ = run.time_launches(200)
-    table["launch_us"] = ms / 200 * 1e3
+    # far-row penalty: the same 4-D contraction with A where the large configuration has it (the k rows of a TMA box
+    # 8 MB apart, every one in another 2 MB page: half of the bytes a CTA of a pair stages) and with A already in the
+    # layout the transpose-assisted route gives it (rows 512 bytes apart): rate_far = rate_near * (1 - p / 2)
+    ext = dict(a=128, b=128, c=128, d=128, e=128, f=32)
+    far, _ = _rate(tc, api, torch, ("abcd", "aebf", "cfde"), ext, F32, iters=3)
+    near, _ = _rate(tc, api, torch, ("abcd", "afeb", "cfde"), ext, F32, iters=3)
+    table["far_row_penalty"] = max(0.0, min(1.0, 2.0 * (1.0 - far / max(near, 1e-9))))
+    # what one more kernel costs in a chain of back-to-back launches: a permutation too small to matter
+    tiny = torch.zeros(4096, device="cuda", dtype=torch.float32)
+    tiny2 = torch.zeros_like(tiny)
+    for _ in range(20):
+        api.transpose(tiny.data_ptr(), tiny2.data_ptr(), [64, 64], [1, 0], 4, stream)
+    e0.record()
+    for _ in range(500):
+        api.transpose(tiny.data_ptr(), tiny2.data_ptr(), [64, 64], [1, 0], 4, stream)
+    e1.record()
+    torch.cuda.synchronize()
+    table["launch_us"] = e0.elapsed_time(e1) / 500 * 1e3
 
     # ---- for the record: rates of the helper kernels (CUDA events; read + write bytes over time) ----
     def permute_gbs(extent, perm, dtype, iters=10):

@@ -263,6 +263,7 @@ void fill_operand_dev(const UmmaOperand& o, UmmaOperandDev* d)
     d->slabs_per_op = o.slabs_per_op;
     d->digit0_scale = o.digit0_scale;
     d->k0_scale = o.k0_scale;
+    d->chunk_digit = o.chunk_digit;
     d->oob_coord = o.oob_coord;
     for (int i = 0; i < kMaxTmaRank; ++i) {
         d->row_digit_dim[i] = i < o.n_row_digits ? o.row_digit_dim[i] : -1;
@@ -339,6 +340,7 @@ tcontb_status finish_run(tcontb_run* run)
         run->umma.BK = u.BK;
         run->umma.stages = u.stages;
         run->umma.pair = u.pair ? 1 : 0;
+        run->umma.store_across_slabs = u.store_across_slabs ? 1 : 0;
         run->umma.n_k_digits = u.n_k_digits;
         for (int i = 0; i < 3; ++i) run->umma.k_digit_ext[i] = static_cast<int>(u.k_digit_ext[i]);
         run->umma.k_iters = static_cast<int>(u.k_iters);

@@ -217,7 +217,7 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                                 const uint32_t e = static_cast<uint32_t>(o.row_digit_ext[d]);
                                 const int idx = static_cast<int>(rem % e);
                                 rem /= e;
-                                const int v = d == 0 ? idx * o.digit0_scale : idx;
+                                const int v = d == o.chunk_digit ? idx * o.digit0_scale : idx;
     #pragma unroll
                                 for (int t = 0; t < kMaxTmaRank; ++t)
                                     if (o.row_digit_dim[d] == t) base[t] = v;
@@ -227,7 +227,7 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                         // Slab beyond the tensor: start the box past the slab mode's end, TMA fills zeros.
     #pragma unroll
                         for (int t = 0; t < kMaxTmaRank; ++t)
-                            if (o.row_digit_dim[0] == t) base[t] = o.oob_coord;
+                            if (o.row_digit_dim[o.chunk_digit] == t) base[t] = o.oob_coord;
                     }
                 }
                 int kd0 = w.it0 % p.k_digit_ext[0], kd1 = (w.it0 / p.k_digit_ext[0]) % p.k_digit_ext[1];
@@ -400,6 +400,37 @@ dmma_tma_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
 #pragma unroll
             for (int j = 0; j < NF; ++j)
                 cn[j] = ld_shared_s64(col_tab + (static_cast<uint32_t>(wn * NF * 8 + 16 * (j >> 1) + (j & 1)) + 2u * fr) * 8u);
+            if (p.store_across_slabs) {
+                // The warp's 64 rows are four slabs of 16; slab q is index a0 + q of C's stride-1 mode and the rows
+                // of a slab run along another mode.  Row (4 fk + dd) of the four slabs is four neighbouring
+                // elements of C: acc[2 q + (dd & 1)][j][dd >> 1], q = 0..3.
+#pragma unroll
+                for (int dd = 0; dd < 4; ++dd) {
+                    const int par = dd & 1, h = dd >> 1;
+                    const uint32_t r = static_cast<uint32_t>(wm * 64) + 4u * fk + static_cast<uint32_t>(dd);
+                    const long long cm0 = ld_shared_s64(row_tab + r * 8u), cm1 = ld_shared_s64(row_tab + (r + 16u) * 8u);
+                    const long long cm2 = ld_shared_s64(row_tab + (r + 32u) * 8u), cm3 = ld_shared_s64(row_tab + (r + 48u) * 8u);
+                    const bool run4 = cm0 >= 0 && cm1 == cm0 + 1 && cm2 == cm0 + 2 && cm3 == cm0 + 3;
+#pragma unroll
+                    for (int j = 0; j < NF; ++j) {
+                        if (tile_ok && cn[j] >= 0) {
+                            double* dst = C + cm0 + cn[j];
+                            if (run4 && (reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
+                                st_global_cs_v4f64(dst, acc[par][j][h], acc[2 + par][j][h], acc[4 + par][j][h], acc[6 + par][j][h]);
+                            } else {
+                                if (cm0 >= 0) __stcs(dst, acc[par][j][h]);
+                                if (cm1 >= 0) __stcs(C + cm1 + cn[j], acc[2 + par][j][h]);
+                                if (cm2 >= 0) __stcs(C + cm2 + cn[j], acc[4 + par][j][h]);
+                                if (cm3 >= 0) __stcs(C + cm3 + cn[j], acc[6 + par][j][h]);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+#pragma unroll
+                    for (int j = 0; j < NF; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+            } else
 #pragma unroll
             for (int pr = 0; pr < 4; ++pr) {
                 const uint32_t r = static_cast<uint32_t>(wm * 64 + 16 * pr) + 4u * fk;

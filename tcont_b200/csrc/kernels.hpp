@@ -47,6 +47,7 @@ constexpr int kMaxOwners = 8;  // GPUs of one box
 struct UmmaOperandDev {
     int major, slab_w, slabs_per_tile, n_row_digits, slab_bytes;
     int slabs_per_op, digit0_scale, oob_coord;
+    int chunk_digit;  // which row digit is the chunk of the slab mode (scaled by digit0_scale, out-of-range past the tensor)
     int k0_scale;  // TMA coordinate of k digit 0 = k iteration * this
     int row_digit_dim[kMaxTmaRank];
     int row_digit_ext[kMaxTmaRank];
@@ -85,6 +86,7 @@ struct UmmaParams {
     // into the memory of the GPU that owns it, over NVLink: element i of the full C (i inside range o) goes to
     // owner_base[o][i].  owners = 0 or 1: everything goes to C.  `tn_rotate` shifts the order in which a GPU
     // visits the tile columns, so that the GPUs of a job write to different owners at any one time.
+    int store_across_slabs;  // FP64 kernel: see UmmaSpec
     int owners, tn_per_owner, tn_rotate;
     float* owner_base[kMaxOwners];
 };

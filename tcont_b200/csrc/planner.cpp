@@ -227,8 +227,10 @@ bool stage_operand(const Problem& p, const std::vector<int>& t, const std::vecto
     return true;
 }
 
+// `lead_mode` >= 0: that row mode becomes digit 0 of the slab index, in front of the chunk digit, so that the
+// slabs of a tile are consecutive indices of it (see rows_across_slabs).
 void finish_operand(const Problem& p, const std::vector<int>& t, const std::vector<int>& rows, int tile_rows, int BK,
-                    const std::vector<int>& kdigits, UmmaOperand* o, int max_slab_rows = 256)
+                    const std::vector<int>& kdigits, UmmaOperand* o, int max_slab_rows = 256, int lead_mode = -1)
 {
     const int elt = p.scalar_type == 1 ? 8 : 4, W = 128 / elt;
     if (o->major == 0) {
@@ -252,13 +254,26 @@ void finish_operand(const Problem& p, const std::vector<int>& t, const std::vect
     o->slabs_per_tile = tile_rows / o->slab_w;
     const int slab_mode = t[static_cast<size_t>(o->slab_dim)];
     o->n_row_digits = 0;
-    o->row_digit_dim[0] = o->slab_dim;
-    o->row_digit_ext[0] = ceil_div(o->slab_mode_ext, o->slab_w);
-    o->row_digit_cstride[0] = o->row_elem_cstride * o->slab_w;
-    o->n_row_digits = 1;
-    o->total_slabs = o->row_digit_ext[0];
+    o->chunk_digit = 0;
+    o->total_slabs = 1;
+    if (lead_mode >= 0) {
+        const Mode& m = p.modes[static_cast<size_t>(lead_mode)];
+        o->row_digit_dim[0] = index_of(t, lead_mode);
+        o->row_digit_ext[0] = m.extent;
+        o->row_digit_cstride[0] = m.sC;
+        o->n_row_digits = 1;
+        o->chunk_digit = 1;
+        o->total_slabs = m.extent;
+    }
+    {
+        const int n = o->n_row_digits++;
+        o->row_digit_dim[n] = o->slab_dim;
+        o->row_digit_ext[n] = ceil_div(o->slab_mode_ext, o->slab_w);
+        o->row_digit_cstride[n] = o->row_elem_cstride * o->slab_w;
+        o->total_slabs *= o->row_digit_ext[n];
+    }
     for (int id : rows) {
-        if (id == slab_mode) continue;
+        if (id == slab_mode || id == lead_mode) continue;
         const Mode& m = p.modes[static_cast<size_t>(id)];
         const int n = o->n_row_digits++;
         o->row_digit_dim[n] = index_of(t, id);
@@ -292,7 +307,7 @@ void finish_operand(const Problem& p, const std::vector<int>& t, const std::vect
 void merge_slabs(UmmaOperand* o, int BK, int cta_slabs)
 {
     const int W = o->slab_w;  // 32 floats or 16 doubles
-    if (o->major != 1 || o->rank > kMaxTmaRank - 1 || o->slab_dim != 0 || o->slab_mode_ext % W) return;
+    if (o->major != 1 || o->rank > kMaxTmaRank - 1 || o->slab_dim != 0 || o->slab_mode_ext % W || o->slabs_per_op > 1) return;
     const int64_t chunks = o->slab_mode_ext / W;
     int g = 1;
     while (g * 2 <= cta_slabs && chunks % (g * 2) == 0 && cta_slabs % (g * 2) == 0) g *= 2;
@@ -469,6 +484,28 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
 
     u->BM = 128;
     finish_operand(p, p.A, p.M, u->BM, BK, kdigits, &u->a);
+    // Rows across slabs (FP64 kernel): A is MN-major on a mode that is not C's stride-1 mode (reference cases 3,
+    // 4, 6-8: C[a,...] from A[d,...,a]).  Rows that run along A's stride-1 mode alone would be stored element by
+    // element, and moving a 200-300 MB A through a transpose first costs more than the contraction.  Instead a
+    // tile is 8 slabs of 16 rows: 16 consecutive elements of A's stride-1 mode (one 128-byte TMA row) times 8
+    // consecutive indices of C's stride-1 mode, fetched by ONE box that spans both modes, and a thread stores
+    // the same row of four neighbouring slabs as one 32-byte piece of C.  Needs C's stride-1 mode behind the
+    // chunked contracted mode in A's memory order (the box then lands slab by slab) and an extent that is a
+    // multiple of 8 (a tile never wraps to the next chunk).
+    int lead_a = -1;
+    if (f64 && u->a.major == 1 && u->a.row_elem_cstride != 1 && split_inner[0] == 0 && !p.M.empty() && !std::getenv("TCONT_NO_ROWS_ACROSS_SLABS")) {
+        const int c1 = p.M[0];
+        const Mode& m1 = p.modes[static_cast<size_t>(c1)];
+        const int dim1 = index_of(p.A, c1);
+        if (m1.sC == 1 && dim1 > u->a.kc_dim && dim1 != u->a.slab_dim && m1.extent % 8 == 0) {
+            lead_a = c1;
+            u->a.slab_w = 16;
+            finish_operand(p, p.A, p.M, u->BM, BK, kdigits, &u->a, 256, lead_a);
+            u->a.box[dim1] = u->a.slabs_per_tile;   // one copy per stage: 8 slabs = 8 indices of C's stride-1 mode
+            u->a.slabs_per_op = u->a.slabs_per_tile;
+            u->store_across_slabs = true;
+        }
+    }
     u->tiles_m = ceil_div(u->a.total_slabs, u->a.slabs_per_tile);
     // N tile: the widest of 256/128/64/32 that is not wider than the (padded) N extent needs and
     // still yields at least one tile per SM; otherwise the narrowest admissible one.
@@ -540,8 +577,9 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
     {
         const double a_bytes = double(u->a.slabs_per_tile) * u->a.slab_bytes;
         const double b_bytes = double(u->b.slabs_per_tile) * u->b.slab_bytes;
-        const bool a_far = u->a.major == 1 && u->a.stride[u->a.kc_dim] * elt >= 65536;
-        const bool b_far = u->b.major == 1 && u->b.stride[u->b.kc_dim] * elt >= 65536;
+        // rows of a box that lie in different 2 MB pages
+        const bool a_far = u->a.major == 1 && u->a.stride[u->a.kc_dim] * elt >= (int64_t(2) << 20);
+        const bool b_far = u->b.major == 1 && u->b.stride[u->b.kc_dim] * elt >= (int64_t(2) << 20);
         u->far_fraction = ((a_far ? a_bytes : 0.0) + (b_far ? b_bytes : 0.0)) / (a_bytes + b_bytes);
     }
     if (!chunk_kmajor(&u->a, BK, u->a.slabs_per_tile) ||
@@ -693,7 +731,8 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
         // (abcdef-dega-gfbc: 37.7 M elements of C, 1.08 ms against 0.10 ms for its coalesced siblings).
         // (runs shorter than 64 bytes count as scattered too: cfg3 cut to a = 6 ran at 17.6 TFLOP/s here
         // against 20.2 on the gather kernel, which sees those rows as one flat index)
-        if (u.a.row_elem_cstride != 1 || u.a.slab_mode_ext < 8) scatter_us = double(p.sizeC) * double(u.k_splits) * c.scatter_store_ps * 1e-6;
+        if ((u.a.row_elem_cstride != 1 && !u.store_across_slabs) || u.a.slab_mode_ext < 8)
+            scatter_us = double(p.sizeC) * double(u.k_splits) * c.scatter_store_ps * 1e-6;
     }
     if (kernel == KERNEL_DMMA_F64) {
         const int64_t bn = p.Ntot <= 48 ? 32 : 64, bm = p.Ntot <= 48 ? 256 : 128;
@@ -1012,7 +1051,8 @@ std::string describe_plan(const Plan& pl)
           << ",\"a_major\":\"" << (u.a.major ? "MN" : "K") << "\",\"b_major\":\"" << (u.b.major ? "MN" : "K") << "\""
           << ",\"a_slab_w\":" << u.a.slab_w << ",\"b_slab_w\":" << u.b.slab_w << ",\"a_slabs_per_copy\":" << u.a.slabs_per_op << ",\"b_slabs_per_copy\":" << u.b.slabs_per_op << ",\"a_slabs\":" << u.a.slabs_per_tile
           << ",\"b_slabs\":" << u.b.slabs_per_tile << ",\"smem_bytes\":" << u.smem_bytes
-          << ",\"coalesced_store\":" << (u.a.row_elem_cstride == 1 ? "true" : "false");
+          << ",\"coalesced_store\":" << (u.a.row_elem_cstride == 1 ? "true" : "false")
+          << ",\"store_across_slabs\":" << (u.store_across_slabs ? "true" : "false");
     }
     o << "}}";
     return o.str();

@@ -64,7 +64,8 @@ struct UmmaOperand {
     int digit0_scale = 32;   // TMA coordinate of row digit 0 = chunk index * this
     int k0_scale = 32;       // TMA coordinate of k digit 0 = k iteration * this (BK; BK / 32 for a K-major operand chunked in 32s)
     int oob_coord = 0;       // coordinate (in row digit 0's dim) that lies past the tensor: zero fill
-    int n_row_digits = 1;  // slab index = mixed radix number; digit 0 = chunk of the slab mode
+    int n_row_digits = 1;  // slab index = mixed radix number; digit `chunk_digit` = chunk of the slab mode
+    int chunk_digit = 0;   // 0 normally; 1 when C's stride-1 mode leads the digits (rows of a tile run across slabs)
     int row_digit_dim[kMaxTmaRank] = {0};
     int64_t row_digit_ext[kMaxTmaRank] = {1};
     int64_t row_digit_cstride[kMaxTmaRank] = {0};  // C offset per unit of the digit
@@ -95,6 +96,9 @@ struct UmmaSpec {
     double far_fraction = 0;  // share of a stage's bytes whose K rows are 64 KB or more apart in memory
     int raster_group = 16;
     bool pair = false;  // two-CTA clusters working on 256-row tiles (tcgen05 cta_group::2)
+    // FP64 kernel: the slabs of an A tile are consecutive indices of C's stride-1 mode (which is not A's stride-1
+    // mode); a thread stores the same row of four neighbouring slabs as one 32-byte piece
+    bool store_across_slabs = false;
     int smem_bytes = 0;
     int elt = 4;  // element bytes: 4 = tcgen05 TF32 kernel, 8 = TMA-fed FP64 tensor-path kernel
 };
@@ -106,22 +110,25 @@ struct SimtSpec {
 };
 
 struct CostTable {
-    // Measured on B200; overridable through the file named by TCONT_COST_TABLE ("key value" lines).
-    double hbm_gbs = 6546.9;
-    double umma_tf32_tflops = 600.0;
-    double simt_f32_tflops = 20.0;
-    double simt_f64_tflops = 11.0;
-    double dmma_f64_tflops = 30.0;          // TMA-fed tensor-path kernel
-    double dmma_f64_gather_tflops = 20.0;   // gather tensor-path kernel, 16-byte gathers
-    double dmma_f64_gather8_tflops = 12.0;  // gather tensor-path kernel, an operand on 8-byte gathers
-    double dmma_f64_gather_narrow_tflops = 4.5;  // gather tensor-path kernel, 256 x 32 tiles (N <= 48)
+    // Defaults: what `python -m tcont_b200.calibrate` measured on a B200 (the file it writes,
+    // tcont_cost_table.NVIDIA_B200.txt beside the library, holds the same figures and is read when the current
+    // device has that name; TCONT_COST_TABLE names another "key value" file).
+    double hbm_gbs = 6207.9;                // copy through the permutation kernel, read + write
+    double umma_tf32_tflops = 687.9;        // tcgen05 kernel, 8192 x 8192 x 4096, CTA pairs with a k chunk of 64
+    double simt_f32_tflops = 23.7;
+    double simt_f64_tflops = 16.4;
+    double dmma_f64_tflops = 33.4;          // TMA-fed tensor-path kernel
+    double dmma_f64_gather_tflops = 20.9;   // gather tensor-path kernel, 16-byte gathers
+    double dmma_f64_gather8_tflops = 15.6;  // gather tensor-path kernel, an operand on 8-byte gathers
+    double dmma_f64_gather_narrow_tflops = 6.5;  // gather tensor-path kernel, 256 x 32 tiles (N <= 48)
     double scatter_store_ps = 28.0;         // per element of C stored on its own (TMA-fed FP64 kernel)
-    double scatter_store_f32_ps = 11.0;     // the same for the tcgen05 kernel's 4-byte elements
-    double launch_us = 3.0;
+    double scatter_store_f32_ps = 13.3;     // the same for the tcgen05 kernel's 4-byte elements
+    double launch_us = 3.0;                 // one more kernel in a chain of back-to-back launches
+    // Fraction of the tcgen05 rate lost per unit of staged bytes whose K rows lie 2 MB or more apart, i.e. every row
+    // of a TMA box in another 2 MB page (cfg5 where it lies, A's rows 8 MB apart, half of a pair's bytes: 424 TFLOP/s
+    // against 587 after the transpose that brings them together; with rows 1 MB apart there is no loss: 701 / 689).
+    double far_row_penalty = 0.55;
     int num_sms = 148;  // SMs of the device the plan is made for (api.cpp fills it in from the current device)
-    // Fraction of the tcgen05 rate lost per unit of staged bytes whose K rows lie 64 KB or more apart
-    // (cfg5 on B200: 274 / 434 / 605 TFLOP/s with two thirds / one third / none of the bytes far-strided).
-    double far_row_penalty = 0.85;
 };
 
 struct Plan {

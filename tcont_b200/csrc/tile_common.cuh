@@ -165,7 +165,7 @@ __device__ __forceinline__ long long slab_c_offset(const UmmaOperandDev& o, uint
             const uint32_t idx = rem % e;
             rem /= e;
             off += static_cast<long long>(idx) * o.row_digit_cstride[d];
-            if (d == 0) *digit0 = static_cast<int>(idx);
+            if (d == o.chunk_digit) *digit0 = static_cast<int>(idx);
         }
     }
     return off;

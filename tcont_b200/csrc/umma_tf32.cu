@@ -237,7 +237,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                             const uint32_t e = static_cast<uint32_t>(o.row_digit_ext[d]);
                             const int idx = static_cast<int>(rem % e);
                             rem /= e;
-                            const int v = d == 0 ? idx * o.digit0_scale : idx;
+                            const int v = d == o.chunk_digit ? idx * o.digit0_scale : idx;
 #pragma unroll
                             for (int t = 0; t < kMaxTmaRank; ++t)
                                 if (o.row_digit_dim[d] == t) base[t] = v;
@@ -247,7 +247,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                     // Slab beyond the tensor: start the box past the slab mode's end, TMA fills zeros.
 #pragma unroll
                     for (int t = 0; t < kMaxTmaRank; ++t)
-                        if (o.row_digit_dim[0] == t) base[t] = o.oob_coord;
+                        if (o.row_digit_dim[o.chunk_digit] == t) base[t] = o.oob_coord;
                 }
             }
             // K digits: chunk of the chunked mode, then the other K modes

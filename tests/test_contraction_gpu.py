@@ -524,3 +524,24 @@ def test_cta_pairs_with_k_chunks_of_64(engine, oracle, monkeypatch, name):
     assert desc["kernel"] == "umma_tf32" and u["pair"] is True and u["BN"] == 256, u
     assert u["BK"] == (32 if name == "k_not_32" else 64), u
     check(oracle, c, A, B, out, desc)
+
+
+ACROSS_SLABS_SHAPES = {
+    # FP64, A MN-major on a mode that is not C's stride-1 mode (reference cases 3, 4, 6-8 and 1): tiles of
+    # 16 elements of A's stride-1 mode x 8 indices of C's stride-1 mode, stored across slabs
+    "case3_like": Contraction("abcd", "dbea", "ec", dict(a=24, b=6, c=24, d=40, e=40), F64),        # ragged slab mode (40 = 2.5 x 16), K tail
+    "case4_like": Contraction("abcd", "deca", "be", dict(a=16, b=24, c=10, d=48, e=24), F64),
+    "case6_like": Contraction("abcde", "efbad", "cf", dict(a=16, b=4, c=24, d=4, e=32, f=32), F64),  # 5-D box
+    "case7_like": Contraction("abcde", "ecbfa", "fd", dict(a=8, b=6, c=5, d=24, e=48, f=24), F64),
+    "case1_like": Contraction("abc", "bda", "dc", dict(a=64, b=56, c=24, d=56), F64),
+    "wide_n": Contraction("abcd", "dbea", "ec", dict(a=32, b=5, c=100, d=32, e=16), F64),            # more than one tile column
+}
+
+
+@pytest.mark.parametrize("name", list(ACROSS_SLABS_SHAPES))
+def test_fp64_rows_across_slabs(engine, oracle, name):
+    c = ACROSS_SLABS_SHAPES[name]
+    A, B = oracle.inputs(c, 71, -1.0, 1.0)
+    out, desc = run_contraction(engine, c, A, B, 1, launches=2)
+    assert desc["kernel"] == "dmma_f64_tma" and desc["umma"]["store_across_slabs"] is True, desc["umma"]
+    check(oracle, c, A, B, out, desc)

@@ -66,14 +66,20 @@ def test_configs_pick_the_intended_kernels(engine):
 
 def test_fp64_kernel_choice_follows_the_cost_table(engine, monkeypatch):
     F64 = 1
-    # a slab mode that is not C's stride-1 mode: stores would be scattered, one transpose of A is cheaper
+    # A's stride-1 mode is not C's: where C's stride-1 mode lies behind the contracted mode in A and its extent is a
+    # multiple of 8, a tile takes 8 of its indices x 16 elements of A's stride-1 mode and stores across slabs
     c31 = Contraction("abcdef", "dega", "gfbc", dict(a=24, b=16, c=16, d=24, e=16, f=16, g=24), F64)
     d = describe(engine, c31)
-    assert d["backend"] == "ttgt" and d["kernel"] == "dmma_f64_tma" and d["umma"]["coalesced_store"]
-    # ... unless the contracted extent is long enough to pay for them (and A is too large to move)
+    assert d["backend"] == "direct" and d["kernel"] == "dmma_f64_tma" and d["umma"]["store_across_slabs"]
+    assert d["umma"]["a_slabs_per_copy"] == 8 and not d["umma"]["coalesced_store"]
     c1 = Contraction("abc", "bda", "dc", dict(a=312, b=312, c=24, d=312), F64)
     d = describe(engine, c1)
-    assert d["backend"] == "direct" and d["kernel"] == "dmma_f64_tma" and not d["umma"]["coalesced_store"]
+    assert d["backend"] == "direct" and d["kernel"] == "dmma_f64_tma" and d["umma"]["store_across_slabs"]
+    # ... where it cannot (extent 30 is no multiple of 8), rows along A's stride-1 mode would be stored element by
+    # element, and one transpose of A is cheaper
+    c31r = Contraction("abcdef", "dega", "gfbc", dict(a=30, b=16, c=16, d=24, e=16, f=16, g=24), F64)
+    d = describe(engine, c31r)
+    assert d["backend"] == "ttgt" and d["kernel"] == "dmma_f64_tma" and d["umma"]["coalesced_store"] and not d["umma"]["store_across_slabs"]
     # operands that are K-major on different contracted modes cannot be described to TMA where they lie
     c28 = Contraction("abcd", "eafb", "fdec", dict(a=72, b=72, c=72, d=72, e=72, f=72), F64)
     d = describe(engine, c28)
