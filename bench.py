@@ -267,7 +267,7 @@ def parity_verdict(job, local_eq, A, B, out, kernel, seed):
     c = Contraction(local_eq.modeC, local_eq.modeA, local_eq.modeB, dict(local_eq.extent), int(local_eq.scalar_type))
     oracle = Oracle()
     oracle.set_num_threads(max(1, len(os.sched_getaffinity(0)) // job.world))
-    n = min(PARITY_SAMPLES, out.size)
+    n = min(max(PARITY_SAMPLES // job.world, 20_000), out.size)     # PARITY_SAMPLES over the whole job, 20 000 per rank at least
     idx = np.sort(np.random.default_rng(seed + 17 * job.rank).integers(0, out.size, size=n)) if n < out.size else np.arange(out.size)
     got = out[idx].astype(np.float64)
     finite = bool(np.isfinite(got).all())
@@ -305,7 +305,7 @@ def contracted_parity(job, full_eq, A, B, mine, first, kernel, seed):
     c = Contraction(full_eq.modeC, full_eq.modeA, full_eq.modeB, dict(full_eq.extent), int(full_eq.scalar_type))
     oracle = Oracle()
     oracle.set_num_threads(max(1, len(os.sched_getaffinity(0)) // job.world))
-    n = min(PARITY_SAMPLES // job.world, mine.size)
+    n = min(max(PARITY_SAMPLES // job.world, 20_000), mine.size)
     local = np.sort(np.random.default_rng(seed + 31 * job.rank).integers(0, mine.size, size=n))
     idx = local + first
     got = mine[local].astype(np.float64)

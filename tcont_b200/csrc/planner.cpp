@@ -609,10 +609,16 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
         const int64_t wave = f64 ? 2 * cost.num_sms : u->pair ? cost.num_sms / 2 : cost.num_sms;
         const double flops = 2.0 * double(u->tiles_m * u->BM) * double(u->tiles_n * u->BN) * double(u->k_iters * u->BK);
         const double rate = (f64 ? cost.dmma_f64_tflops : cost.umma_tf32_tflops) * 1e6;  // flops per microsecond
+        // The tcgen05 kernel's ring advances by one stage per `umma_stage_us` at best, whatever the stage holds (the
+        // producer's wait-announce-copy round trip): a work unit takes at least its stages times that, which is what
+        // a long k loop on narrow tiles costs, not its flops.
         auto estimate = [&](int64_t s) {
             const int64_t units = tiles * s;
-            const double eff = double(units) / double(ceil_div(units, wave) * wave);
-            return flops / (rate * eff) + (s > 1 ? cost.launch_us + 2.0 * double(s) * double(p.sizeC) * elt / (cost.hbm_gbs * 1e3) : 0.0);
+            const int64_t rounds = ceil_div(units, wave);
+            const double eff = double(units) / double(rounds * wave);
+            double t = flops / (rate * eff);
+            if (!f64) t = std::max(t, double(rounds) * double(ceil_div(u->k_iters, s)) * cost.umma_stage_us);
+            return t + (s > 1 ? cost.launch_us + 2.0 * double(s) * double(p.sizeC) * elt / (cost.hbm_gbs * 1e3) : 0.0);
         };
         int64_t splits = 1;
         if (tiles < 4 * wave && u->k_iters >= 8) {
@@ -709,7 +715,7 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
     const double flops = 2.0 * double(p.Mtot) * double(p.Ntot) * double(p.Ktot);
     double c_bytes = double(p.sizeC) * elt;
     double rate = p.scalar_type == 1 ? c.simt_f64_tflops : c.simt_f32_tflops;
-    double extra_us = 0, scatter_us = 0;
+    double extra_us = 0, scatter_us = 0, extra_floor_us = 0;
     // tiles are computed whole: the work of an FP64 kernel is that of the extents rounded up to its tile
     auto padded = [&](int64_t bm, int64_t bn) {
         return double(ceil_div(p.Mtot, bm) * bm) / double(p.Mtot) * double(ceil_div(p.Ntot, bn) * bn) / double(p.Ntot);
@@ -749,11 +755,15 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
         // Rows of a slab that are not contiguous in C are stored element by element, a 32-byte sector each
         // (abcd-dbea-ec, 9.0 M elements of C: 0.125 ms against a 0.022 ms traffic floor).
         if (u.a.row_elem_cstride != 1) scatter_us = double(p.sizeC) * double(u.k_splits) * c.scatter_store_f32_ps * 1e-6;
+        // (one stage per umma_stage_us at best: see plan_umma_impl)
+        const int64_t units = (u.pair ? ceil_div(u.tiles_m, 2) : u.tiles_m) * u.tiles_n * u.k_splits;
+        const int64_t wave = u.pair ? c.num_sms / 2 : c.num_sms;
+        extra_floor_us = double(ceil_div(units, wave)) * double(u.k_iters_per_split) * c.umma_stage_us;
     }
     const double bytes = (double(p.sizeA) + double(p.sizeB)) * elt + c_bytes;
     // scattered stores are a third ceiling rather than an addition: one consumer group stores while the
     // other computes (abc-bda-dc, K = 312: 0.086 ms scattered against 0.072 ms for its coalesced sibling)
-    return c.launch_us + std::max({flops / (rate * 1e6), bytes / (c.hbm_gbs * 1e3), scatter_us}) + extra_us;
+    return c.launch_us + std::max({flops / (rate * 1e6), bytes / (c.hbm_gbs * 1e3), scatter_us, extra_floor_us}) + extra_us;
 }
 
 // TF32 goes to the tcgen05 kernel whenever its tiles can be described to TMA.  FP64 takes the
@@ -806,6 +816,7 @@ bool read_cost_table_file(const std::string& path, CostTable* table)
         else if (key == "scatter_store_ps") c.scatter_store_ps = v;
         else if (key == "scatter_store_f32_ps") c.scatter_store_f32_ps = v;
         else if (key == "far_row_penalty") c.far_row_penalty = v;
+        else if (key == "umma_stage_us") c.umma_stage_us = v;
         else if (key == "num_sms" && v >= 1) c.num_sms = static_cast<int>(v);
     }
     return true;

@@ -128,6 +128,9 @@ struct CostTable {
     // of a TMA box in another 2 MB page (cfg5 where it lies, A's rows 8 MB apart, half of a pair's bytes: 424 TFLOP/s
     // against 587 after the transpose that brings them together; with rows 1 MB apart there is no loss: 701 / 689).
     double far_row_penalty = 0.55;
+    // Least time per stage of the tcgen05 kernel's ring, whatever the stage holds: one pass of the producer's
+    // wait-announce-copy sequence (700 to 900 cycles in the main-loop probes).
+    double umma_stage_us = 0.45;
     int num_sms = 148;  // SMs of the device the plan is made for (api.cpp fills it in from the current device)
 };
 
