@@ -66,6 +66,15 @@ const char* tcontb_last_error(void);
  * Replaces the reference's LightGBM selector, Python planner and NVRTC step; nothing is
  * compiled at run time. */
 tcontb_status tcontb_plan_create(const tcontb_desc* desc, tcontb_plan** out);
+/* Beyond the reference, whose descriptor has no strides (backends/cogent/plan/base/index_mapping.py:211 takes
+ * dense column-major tensors): each tensor may be a sub-tensor VIEW of a larger column-major tensor.  parent_x[i] is the
+ * extent of mode i of tensor x in its parent (at least the view's extent; NULL = that tensor is dense).  Strides come from
+ * the parents, everything else from the view's extents; modes fuse only where the view leaves no gap between them.  A
+ * plan over views runs on caller-owned device buffers (tcontb_run_create_on_device), with the pointers at the views'
+ * first elements, 16-byte aligned; split-K, alpha/beta, the compensated Float32 mode, zero_output and copy_output are not
+ * available when C is a view. */
+tcontb_status tcontb_plan_create_strided(const tcontb_desc* desc, const int64_t* parent_c, const int64_t* parent_a,
+                                         const int64_t* parent_b, tcontb_plan** out);
 void tcontb_plan_destroy(tcontb_plan* plan);
 /* ExecutionPlan::backend (tcont.hpp:126): TCONTB_BACKEND_DIRECT prints as "cogent",
  * TCONTB_BACKEND_TTGT as "ttgt". */

@@ -15,7 +15,7 @@ from . import sharding  # noqa: F401
 _API_NAMES = (
     "Backend", "BackendSelection", "ExecutionPlan", "ExecutionRun", "ScalarType", "TCEquation", "TcontError",
     "compute_gflops", "copy_output_to_host", "fill_uniform", "input_left_host_data", "input_right_host_data",
-    "launch", "library_path", "plan", "prepare", "stage_times", "transpose", "warmup", "zero_output",
+    "launch", "library_path", "plan", "plan_views", "prepare", "stage_times", "transpose", "warmup", "zero_output",
 )
 
 

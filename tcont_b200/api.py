@@ -61,6 +61,8 @@ class _Desc(C.Structure):
 
 _lib.tcontb_last_error.restype = C.c_char_p
 _lib.tcontb_plan_create.argtypes = [C.POINTER(_Desc), C.POINTER(C.c_void_p)]
+_lib.tcontb_plan_create_strided.argtypes = [C.POINTER(_Desc), C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64),
+                                            C.POINTER(C.c_void_p)]
 _lib.tcontb_plan_destroy.argtypes = [C.c_void_p]
 _lib.tcontb_plan_backend.argtypes = [C.c_void_p]
 _lib.tcontb_plan_describe.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t]
@@ -229,6 +231,29 @@ def plan(desc: TCEquation) -> ExecutionPlan:
               int(desc.backend_selection))
     h = C.c_void_p()
     _check(_lib.tcontb_plan_create(C.byref(d), C.byref(h)))
+    return ExecutionPlan(h, desc)
+
+
+def plan_views(desc: TCEquation, parent_c=None, parent_a=None, parent_b=None) -> ExecutionPlan:
+    """tcontb_plan_create_strided: the tensors are sub-tensor views of larger column-major tensors; parent_x lists
+    the extents of tensor x's modes in its parent (None = dense).  Run it with prepare_on_device on pointers at the
+    views' first elements."""
+    modes = "".join(sorted(desc.extent))
+    vals = (C.c_int64 * max(1, len(modes)))(*[int(desc.extent[m]) for m in modes])
+    d = _Desc(len(desc.modeC), len(desc.modeA), len(desc.modeB), desc.modeC.encode(), desc.modeA.encode(),
+              desc.modeB.encode(), desc.op.encode()[:1] or b"?", int(desc.scalar_type), len(modes), modes.encode(), vals,
+              int(desc.backend_selection))
+
+    def arr(p, n):
+        if p is None:
+            return None
+        if len(p) != n:
+            raise ValueError("parent extents must be given for every mode of the tensor")
+        return (C.c_int64 * n)(*[int(x) for x in p])
+
+    h = C.c_void_p()
+    _check(_lib.tcontb_plan_create_strided(C.byref(d), arr(parent_c, len(desc.modeC)), arr(parent_a, len(desc.modeA)),
+                                           arr(parent_b, len(desc.modeB)), C.byref(h)))
     return ExecutionPlan(h, desc)
 
 

@@ -318,13 +318,15 @@ tcontb_status finish_run(tcontb_run* run)
     const void* kB = run->roleB_src();
     run->kernels_per_launch = 1;
     if (pl.tA.needed) {
-        if (!make_transpose_params(pl.tA.rank, pl.tA.src_extent, pl.tA.perm, &run->tpA)) return fail(TCONTB_RUNTIME_ERROR, "bad transpose plan for A");
+        if (!make_transpose_params(pl.tA.rank, pl.tA.src_extent, pl.tA.perm, &run->tpA, pl.tA.strided_src ? pl.tA.src_stride : nullptr))
+            return fail(TCONTB_RUNTIME_ERROR, "bad transpose plan for A");
         TC_CUDA(run->tbufA.alloc(static_cast<size_t>(pl.tA.elements) * run->elt));
         kA = run->tbufA.ptr;
         run->kernels_per_launch++;
     }
     if (pl.tB.needed) {
-        if (!make_transpose_params(pl.tB.rank, pl.tB.src_extent, pl.tB.perm, &run->tpB)) return fail(TCONTB_RUNTIME_ERROR, "bad transpose plan for B");
+        if (!make_transpose_params(pl.tB.rank, pl.tB.src_extent, pl.tB.perm, &run->tpB, pl.tB.strided_src ? pl.tB.src_stride : nullptr))
+            return fail(TCONTB_RUNTIME_ERROR, "bad transpose plan for B");
         TC_CUDA(run->tbufB.alloc(static_cast<size_t>(pl.tB.elements) * run->elt));
         kB = run->tbufB.ptr;
         run->kernels_per_launch++;
@@ -352,7 +354,7 @@ tcontb_status finish_run(tcontb_run* run)
         run->umma.split_stride = pl.sizeC;
         void* out = run->dC;
         const char* x3 = std::getenv("TCONT_TF32X3");
-        run->tf32x3 = pl.kernel == KERNEL_UMMA_TF32 && x3 && x3[0] == '1';
+        run->tf32x3 = pl.kernel == KERNEL_UMMA_TF32 && x3 && x3[0] == '1' && !p.strided;
         if (u.k_splits > 1 || run->tf32x3) {
             TC_CUDA(run->splitk.alloc(static_cast<size_t>(run->tf32x3 ? 3 : 1) * static_cast<size_t>(u.k_splits) *
                                       static_cast<size_t>(pl.sizeC) * run->elt));
@@ -739,6 +741,19 @@ tcontb_status tcontb_plan_create(const tcontb_desc* d, tcontb_plan** out)
     return TCONTB_OK;
 }
 
+tcontb_status tcontb_plan_create_strided(const tcontb_desc* d, const int64_t* parent_c, const int64_t* parent_a, const int64_t* parent_b,
+                                         tcontb_plan** out)
+{
+    if (!d || !out) return fail(TCONTB_INVALID_ARGUMENT, "Null descriptor or output pointer");
+    std::unique_ptr<tcontb_plan> pl(new tcontb_plan());
+    std::string err;
+    const int rc = make_plan(d->modeC, d->nC, d->modeA, d->nA, d->modeB, d->nB, d->op, d->scalar_type, d->ext_mode, d->ext_val,
+                             d->n_ext, d->backend_selection, device_cost_table(), &pl->plan, &err, parent_c, parent_a, parent_b);
+    if (rc) return fail(static_cast<tcontb_status>(rc), err);
+    *out = pl.release();
+    return TCONTB_OK;
+}
+
 void tcontb_plan_destroy(tcontb_plan* plan) { delete plan; }
 
 int tcontb_plan_backend(const tcontb_plan* plan) { return plan ? plan->plan.backend : -1; }
@@ -772,6 +787,8 @@ tcontb_status tcontb_run_create_with_inputs(const tcontb_plan* plan, const void*
 {
     if (!out) return fail(TCONTB_INVALID_ARGUMENT, "Null output pointer");
     if (!a_host || !b_host) return fail(TCONTB_INVALID_ARGUMENT, "Null input buffer");
+    if (plan && plan->plan.prob.strided)
+        return fail(TCONTB_UNSUPPORTED, "a plan over sub-tensor views runs on caller-owned device buffers (tcontb_run_create_on_device)");
     std::unique_ptr<tcontb_run> run;
     tcontb_status st = new_run(plan, &run);
     if (st != TCONTB_OK) return st;
@@ -851,6 +868,7 @@ tcontb_status tcontb_run_upload_inputs(tcontb_run* run, const void* a_host, cons
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
     if (!a_host || !b_host) return fail(TCONTB_INVALID_ARGUMENT, "Null input buffer");
     TC_NOT_SHARDED(run, "replacing the inputs");
+    if (run->plan.prob.strided) return fail(TCONTB_UNSUPPORTED, "replacing the inputs is not available on sub-tensor views");
     const Plan& pl = run->plan;
     TC_CUDA(cudaMemcpyAsync(run->dL, a_host, static_cast<size_t>(pl.sizeL) * run->elt, cudaMemcpyHostToDevice, run->stream));
     TC_CUDA(cudaMemcpyAsync(run->dR, b_host, static_cast<size_t>(pl.sizeR) * run->elt, cudaMemcpyHostToDevice, run->stream));
@@ -863,6 +881,7 @@ tcontb_status tcontb_run_set_scalars(tcontb_run* run, double alpha, double beta)
     if (!std::isfinite(alpha) || !std::isfinite(beta)) return fail(TCONTB_INVALID_ARGUMENT, "alpha and beta must be finite");
     TC_NOT_SHARDED(run, "alpha and beta");
     const bool scaled = alpha != 1.0 || beta != 0.0;
+    if (scaled && run->plan.prob.c_strided) return fail(TCONTB_UNSUPPORTED, "alpha and beta are not available when C is a sub-tensor view");
     if (scaled && !run->splitk.ptr && !run->scaled_ws.ptr) {
         // allocated here, once, so that launches stay free of allocations
         TC_CUDA(run->scaled_ws.alloc(static_cast<size_t>(run->plan.sizeC) * run->elt));
@@ -1008,6 +1027,7 @@ tcontb_status tcontb_run_zero_output(tcontb_run* run)
         TC_CUDA(cudaSetDevice(run->first_device));
         return TCONTB_OK;
     }
+    if (run->plan.prob.c_strided) return fail(TCONTB_UNSUPPORTED, "zero_output is not available when C is a sub-tensor view (the caller owns the parent tensor)");
     TC_CUDA(cudaMemsetAsync(run->dC, 0, static_cast<size_t>(run->plan.sizeC) * run->elt, run->stream));
     return TCONTB_OK;
 }
@@ -1046,6 +1066,7 @@ tcontb_status tcontb_run_copy_output(tcontb_run* run, void* dst, size_t bytes)
 {
     if (!run) return fail(TCONTB_INVALID_ARGUMENT, "ExecutionRun is empty");
     if (!dst) return fail(TCONTB_INVALID_ARGUMENT, "Destination buffer is null");
+    if (run->plan.prob.c_strided) return fail(TCONTB_UNSUPPORTED, "copy_output is not available when C is a sub-tensor view (the caller owns the parent tensor)");
     const size_t have = static_cast<size_t>(run->plan.sizeC) * run->elt;
     if (bytes > have) return fail(TCONTB_INVALID_ARGUMENT, "Requested more bytes than the output tensor holds");
     if (!run->shards.empty()) {
@@ -1108,6 +1129,7 @@ tcontb_status tcontb_run_contract_host(tcontb_run* run, const void* a_host, cons
     if (!c_host) return fail(TCONTB_INVALID_ARGUMENT, "Destination buffer is null");
     TC_NOT_SHARDED(run, "the host-buffer pass");
     if (!a_host || !b_host) return fail(TCONTB_INVALID_ARGUMENT, "Null input buffer");
+    if (run->plan.prob.strided) return fail(TCONTB_UNSUPPORTED, "the host-buffer pass is not available on sub-tensor views");
     if (!run->pipe.tried) {
         const tcontb_status bs = build_host_pipeline(run);
         if (bs != TCONTB_OK) return bs;
@@ -1197,6 +1219,7 @@ tcontb_status tcontb_run_ksplit_enable(tcontb_run* run, int world, int rank)
     const Plan& pl = run->plan;
     const Problem& p = pl.prob;
     const UmmaSpec& u = pl.umma;
+    if (p.strided) return fail(TCONTB_UNSUPPORTED, "contracted-mode split is not available on sub-tensor views");
     if (pl.kernel != KERNEL_UMMA_TF32 || u.k_splits != 1 || run->tf32x3)
         return fail(TCONTB_UNSUPPORTED, "contracted-mode split needs the tcgen05 kernel without split-K (Float32 operands TMA can stage; TCONT_SPLITK=1)");
     // C's slowest mode must be a column mode of the kernel (role B), the most significant digit of the column

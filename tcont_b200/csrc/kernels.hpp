@@ -38,7 +38,8 @@ struct TransposeParams {
     int64_t elements;
 };
 // Builds merged params for dst mode i = src mode perm[i]; returns false for a bad permutation.
-bool make_transpose_params(int rank, const int64_t* src_extent, const int* perm, TransposeParams* out);
+// `src_stride` (optional): element strides of the source modes when the source is a view into a larger tensor.
+bool make_transpose_params(int rank, const int64_t* src_extent, const int* perm, TransposeParams* out, const int64_t* src_stride = nullptr);
 cudaError_t launch_transpose(const void* src, void* dst, const TransposeParams& p, int elem_bytes, cudaStream_t stream);
 
 // ---- TF32 tcgen05 contraction (umma_tf32.cu) -------------------------------------------------

@@ -37,8 +37,11 @@ int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // Builds the kernel-facing problem from mode strings of C, left and right.
 // Returns 0 / 1 (invalid) / 3 (unsupported).
+// `parC` / `parL` / `parR`: for a sub-tensor view, the extents of the tensor's modes in the parent it is a view of
+// (by position; empty = the tensor is dense).
 int build_problem(const std::string& mC, const std::string& mL, const std::string& mR, const std::string& ext_mode,
-                  const std::vector<int64_t>& ext_val, int scalar_type, Problem* out, std::string* err)
+                  const std::vector<int64_t>& ext_val, int scalar_type, Problem* out, std::string* err,
+                  const std::vector<int64_t>& parC = {}, const std::vector<int64_t>& parL = {}, const std::vector<int64_t>& parR = {})
 {
     Problem p;
     p.scalar_type = scalar_type;
@@ -109,6 +112,29 @@ int build_problem(const std::string& mC, const std::string& mL, const std::strin
     p.A = ids(mA);
     p.B = ids(mB);
     p.C = ids(mC);
+    // Element strides, mode by mode, before anything is fused: the product of the extents in front of the mode, taken
+    // from the parent where the tensor is a view of a larger one.
+    const std::vector<int64_t>& parA = p.swapped ? parR : parL;
+    const std::vector<int64_t>& parB = p.swapped ? parL : parR;
+    auto set_strides = [&](const std::vector<int>& t, const std::vector<int64_t>& parent, int which, int64_t* span) -> bool {
+        if (!parent.empty() && parent.size() != t.size()) return false;
+        int64_t st = 1;
+        for (size_t i = 0; i < t.size(); ++i) {
+            Mode& m = p.modes[static_cast<size_t>(t[i])];
+            (which == 0 ? m.sA : which == 1 ? m.sB : m.sC) = st;
+            const int64_t e = parent.empty() ? m.extent : parent[i];
+            if (e < m.extent || e >= (int64_t(1) << 31) || __builtin_mul_overflow(st, e, &st) || st >= (int64_t(1) << 40)) return false;
+        }
+        *span = st;
+        return true;
+    };
+    int64_t spanA = 1, spanB = 1, spanC = 1;
+    if (!set_strides(p.A, parA, 0, &spanA) || !set_strides(p.B, parB, 1, &spanB) || !set_strides(p.C, parC, 2, &spanC)) {
+        *err = "Parent extents of a sub-tensor view must be given for every mode, be at least the view's extents and stay below 2^40 elements";
+        return 1;
+    }
+    p.strided = !parC.empty() || !parL.empty() || !parR.empty();
+    p.c_strided = !parC.empty();
 
     // Fuse y into x when y follows x immediately in every tensor that holds them.
     bool fused = true;
@@ -119,10 +145,17 @@ int build_problem(const std::string& mC, const std::string& mL, const std::strin
                 if (x == y || p.modes[x].group != p.modes[y].group) continue;
                 if (p.modes[x].extent == 0 || p.modes[y].extent == 0) continue;
                 bool ok = true;
+                int which = 0;
                 for (std::vector<int>* t : {&p.A, &p.B, &p.C}) {
                     const int ix = index_of(*t, static_cast<int>(x)), iy = index_of(*t, static_cast<int>(y));
                     if ((ix < 0) != (iy < 0)) ok = false;
                     else if (ix >= 0 && iy != ix + 1) ok = false;
+                    else if (ix >= 0) {   // and y must follow x in memory too (a view may have gaps between them)
+                        const Mode &mx = p.modes[x], &my = p.modes[y];
+                        const int64_t sx = which == 0 ? mx.sA : which == 1 ? mx.sB : mx.sC, sy = which == 0 ? my.sA : which == 1 ? my.sB : my.sC;
+                        if (sy != sx * mx.extent) ok = false;
+                    }
+                    ++which;
                 }
                 if (!ok) continue;
                 p.modes[x].names += p.modes[y].names;
@@ -136,18 +169,18 @@ int build_problem(const std::string& mC, const std::string& mL, const std::strin
             }
         }
     }
-    auto set_strides = [&](const std::vector<int>& t, int which, int64_t* total) {
-        int64_t s = 1;
-        for (int id : t) {
-            Mode& m = p.modes[static_cast<size_t>(id)];
-            (which == 0 ? m.sA : which == 1 ? m.sB : m.sC) = s;
-            s *= m.extent;
-        }
-        *total = s;
+    // element counts of the views (what is read, written and computed); spans are what the strides cover
+    auto count_of = [&](const std::vector<int>& t) {
+        int64_t n = 1;
+        for (int id : t) n *= p.modes[static_cast<size_t>(id)].extent;
+        return n;
     };
-    set_strides(p.A, 0, &p.sizeA);
-    set_strides(p.B, 1, &p.sizeB);
-    set_strides(p.C, 2, &p.sizeC);
+    p.sizeA = count_of(p.A);
+    p.sizeB = count_of(p.B);
+    p.sizeC = count_of(p.C);
+    p.spanA = spanA;
+    p.spanB = spanB;
+    p.spanC = spanC;
 
     for (int id : p.C) {
         if (p.modes[static_cast<size_t>(id)].group == GROUP_M) p.M.push_back(id);
@@ -179,24 +212,28 @@ bool stage_operand(const Problem& p, const std::vector<int>& t, const std::vecto
         o->box[d] = 1;
         o->stride[d] = 0;
     }
-    int64_t s = 1;
+    const int64_t s = is_a ? p.spanA : p.spanB;  // elements the strides cover (the parent's, for a view)
     for (int d = 0; d < o->rank; ++d) {
         const Mode& m = p.modes[static_cast<size_t>(t[static_cast<size_t>(d)])];
         o->ext[d] = m.extent;
-        o->stride[d] = s;
-        s *= m.extent;
+        o->stride[d] = is_a ? m.sA : m.sB;
         if (m.extent >= (int64_t(1) << 31)) {
             *why = "a mode extent does not fit a TMA dimension";
             return false;
         }
+        if (d > 0 && (o->stride[d] * elt) % 16 != 0) {
+            *why = "a stride is not a multiple of 16 bytes (TMA global strides)";
+            return false;
+        }
     }
-    for (int d = o->rank; d < kMaxTmaRank; ++d) o->stride[d] = s;  // padded unit dims
-    if (s * elt >= (int64_t(1) << 40)) {
-        *why = "tensor too large for TMA strides";
+    if (o->rank > 0 && o->stride[0] != 1) {
+        *why = "the first mode is not contiguous";
         return false;
     }
-    if (o->rank >= 2 && (o->ext[0] % (16 / elt)) != 0) {
-        *why = "stride-1 extent is not a multiple of 16 bytes (TMA global strides)";
+    const int64_t pad = (s + 3) / 4 * 4;  // (any multiple of 16 bytes will do)
+    for (int d = o->rank; d < kMaxTmaRank; ++d) o->stride[d] = pad;  // padded unit dims
+    if (s * elt >= (int64_t(1) << 40)) {
+        *why = "tensor too large for TMA strides";
         return false;
     }
     const int first = t[0];
@@ -388,6 +425,7 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
             if (t.size() < 3 || rows.size() < 2 || t[0] != rows[0] || t[1] != rows[1]) continue;
             const Mode m0 = p.modes[static_cast<size_t>(t[0])], m1 = p.modes[static_cast<size_t>(t[1])];
             if (slab_padding_f64(m0.extent) <= 1.08) continue;
+            if ((which == 0 ? m1.sA : m1.sB) != (which == 0 ? m0.sA : m0.sB) * m0.extent) continue;  // (a view with a gap between them)
             Mode f;
             f.names = m0.names + m1.names;
             f.extent = m0.extent * m1.extent;
@@ -621,7 +659,8 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
             return t + (s > 1 ? cost.launch_us + 2.0 * double(s) * double(p.sizeC) * elt / (cost.hbm_gbs * 1e3) : 0.0);
         };
         int64_t splits = 1;
-        if (tiles < 4 * wave && u->k_iters >= 8) {
+        // (a C that is a view into a larger tensor has no workspace "laid out like C" to add partial tiles up in)
+        if (tiles < 4 * wave && u->k_iters >= 8 && !p.c_strided) {
             double best = estimate(1);
             for (int64_t s = 2; s <= std::min<int64_t>(64, u->k_iters / 4); ++s) {
                 if (double(s) * double(p.sizeC) * elt > 512.0 * 1024 * 1024) break;  // workspace
@@ -630,7 +669,7 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
             }
         }
         if (const char* e = std::getenv("TCONT_SPLITK")) {
-            splits = std::max<int64_t>(1, std::min<int64_t>(std::atoll(e), u->k_iters));
+            splits = p.c_strided ? 1 : std::max<int64_t>(1, std::min<int64_t>(std::atoll(e), u->k_iters));
             while (splits > 1 && double(splits) * double(p.sizeC) * elt > 512.0 * 1024 * 1024) --splits;
         }
         u->k_iters_per_split = ceil_div(u->k_iters, splits);
@@ -677,15 +716,19 @@ std::string perm_modes(const Problem& p, const std::vector<int>& ids)
 }
 
 void fill_transpose(const std::string& src, const std::string& dst, const std::string& ext_mode,
-                    const std::vector<int64_t>& ext_val, TransposeSpec* t)
+                    const std::vector<int64_t>& ext_val, TransposeSpec* t, const std::vector<int64_t>& src_parent = {})
 {
     t->needed = src != dst;
     t->rank = static_cast<int>(src.size());
     t->elements = 1;
+    t->strided_src = !src_parent.empty();
+    int64_t st = 1;
     for (size_t i = 0; i < src.size(); ++i) {
         t->src_extent[i] = ext_val[static_cast<size_t>(find_char(ext_mode, src[i]))];
         t->elements *= t->src_extent[i];
         t->perm[i] = find_char(src, dst[i]);
+        t->src_stride[i] = st;   // the source may be a view: strides from its parent's extents
+        st *= src_parent.empty() ? t->src_extent[i] : src_parent[i];
     }
 }
 
@@ -758,7 +801,9 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
         // (one stage per umma_stage_us at best: see plan_umma_impl)
         const int64_t units = (u.pair ? ceil_div(u.tiles_m, 2) : u.tiles_m) * u.tiles_n * u.k_splits;
         const int64_t wave = u.pair ? c.num_sms / 2 : c.num_sms;
-        extra_floor_us = double(ceil_div(units, wave)) * double(u.k_iters_per_split) * c.umma_stage_us;
+        // ... and a tile leaves an SM no faster than the epilogue stores it (cfg4: 7 776 tiles of 128 x 256 in 0.196 ms)
+        const double tile_store_us = double(u.BM) * double(u.BN) * 4.0 / (c.umma_store_gbs_per_sm * 1e3);
+        extra_floor_us = double(ceil_div(units, wave)) * std::max(double(u.k_iters_per_split) * c.umma_stage_us, tile_store_us);
     }
     const double bytes = (double(p.sizeA) + double(p.sizeB)) * elt + c_bytes;
     // scattered stores are a third ceiling rather than an addition: one consumer group stores while the
@@ -817,6 +862,7 @@ bool read_cost_table_file(const std::string& path, CostTable* table)
         else if (key == "scatter_store_f32_ps") c.scatter_store_f32_ps = v;
         else if (key == "far_row_penalty") c.far_row_penalty = v;
         else if (key == "umma_stage_us") c.umma_stage_us = v;
+        else if (key == "umma_store_gbs_per_sm") c.umma_store_gbs_per_sm = v;
         else if (key == "num_sms" && v >= 1) c.num_sms = static_cast<int>(v);
     }
     return true;
@@ -831,7 +877,7 @@ CostTable load_cost_table()
 
 int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* modeB, int nB, char op, int scalar_type,
               const char* ext_mode, const int64_t* ext_val, int n_ext, int backend_selection, const CostTable& cost,
-              Plan* plan, std::string* err)
+              Plan* plan, std::string* err, const int64_t* parentC, const int64_t* parentA, const int64_t* parentB)
 {
     if (!plan || !err) return 1;
     if (nC < 0 || nA < 0 || nB < 0 || n_ext < 0 || nC > kMaxModes || nA > kMaxModes || nB > kMaxModes || n_ext > 64) {
@@ -863,9 +909,12 @@ int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* 
     pl.op = op;
     pl.scalar_type = scalar_type;
     pl.backend_selection = backend_selection;
+    if (parentC) pl.parentC.assign(parentC, parentC + nC);
+    if (parentA) pl.parentA.assign(parentA, parentA + nA);
+    if (parentB) pl.parentB.assign(parentB, parentB + nB);
 
     Problem direct;
-    int rc = build_problem(pl.modeC, pl.modeA, pl.modeB, pl.ext_mode, pl.ext_val, scalar_type, &direct, err);
+    int rc = build_problem(pl.modeC, pl.modeA, pl.modeB, pl.ext_mode, pl.ext_val, scalar_type, &direct, err, pl.parentC, pl.parentA, pl.parentB);
     if (rc) return rc;
     if (direct.sizeA >= (int64_t(1) << 32) || direct.sizeB >= (int64_t(1) << 32)) {
         *err = "Input tensors with 2^32 or more elements are not supported";
@@ -957,15 +1006,20 @@ int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* 
             }
         }
     }
+    // (a transposed operand is a dense scratch tensor; one that is used where it lies keeps its parent's strides)
+    const std::vector<int64_t>& roleA_parent = direct.swapped ? pl.parentB : pl.parentA;
+    const std::vector<int64_t>& roleB_parent = direct.swapped ? pl.parentA : pl.parentB;
+    const std::vector<int64_t> dense;
     Problem ttgt;
-    rc = build_problem(pl.modeC, roleA_dst, roleB_dst, pl.ext_mode, pl.ext_val, scalar_type, &ttgt, err);
+    rc = build_problem(pl.modeC, roleA_dst, roleB_dst, pl.ext_mode, pl.ext_val, scalar_type, &ttgt, err, pl.parentC,
+                       roleA_dst == roleA_src ? roleA_parent : dense, roleB_dst == roleB_src ? roleB_parent : dense);
     if (rc) return rc;
     UmmaSpec ttgt_umma;
     plan_umma(ttgt, cost, &ttgt_umma);
     const int ttgt_kernel = pick_kernel(ttgt, ttgt_umma, cost);
     TransposeSpec tA, tB;
-    fill_transpose(roleA_src, roleA_dst, pl.ext_mode, pl.ext_val, &tA);
-    fill_transpose(roleB_src, roleB_dst, pl.ext_mode, pl.ext_val, &tB);
+    fill_transpose(roleA_src, roleA_dst, pl.ext_mode, pl.ext_val, &tA, roleA_parent);
+    fill_transpose(roleB_src, roleB_dst, pl.ext_mode, pl.ext_val, &tB, roleB_parent);
     const double elt = scalar_type == 1 ? 8.0 : 4.0;
     double t_us = 0;
     if (tA.needed) t_us += cost.launch_us + 2.0 * double(tA.elements) * elt / (cost.hbm_gbs * 0.7 * 1e3);
@@ -1047,6 +1101,7 @@ std::string describe_plan(const Plan& pl)
       << (pl.kernel == KERNEL_UMMA_TF32 ? "umma_tf32" : pl.kernel == KERNEL_DMMA_F64 ? "dmma_f64"
           : pl.kernel == KERNEL_DMMA_F64_TMA ? "dmma_f64_tma" : "simt") << "\""
       << ",\"scalar\":\"" << (pl.scalar_type == 1 ? "f64" : "f32") << "\",\"swapped\":" << (p.swapped ? "true" : "false")
+      << ",\"views\":" << (p.strided ? "true" : "false")
       << ",\"A\":" << list(p.A) << ",\"B\":" << list(p.B) << ",\"C\":" << list(p.C) << ",\"M\":" << list(p.M)
       << ",\"N\":" << list(p.N) << ",\"K\":" << list(p.K) << ",\"Mtot\":" << p.Mtot << ",\"Ntot\":" << p.Ntot
       << ",\"Ktot\":" << p.Ktot << ",\"transpose_a\":" << (pl.tA.needed ? perm(pl.tA) : "null")

@@ -36,7 +36,10 @@ struct Problem {
     std::vector<int> A, B, C;  // mode ids in memory order, fastest first
     std::vector<int> M, N, K;  // M and N in C's order; K in the order the kernels iterate it
     int64_t Mtot = 1, Ntot = 1, Ktot = 1;
-    int64_t sizeA = 1, sizeB = 1, sizeC = 1;
+    int64_t sizeA = 1, sizeB = 1, sizeC = 1;  // elements of the (sub-)tensors
+    int64_t spanA = 1, spanB = 1, spanC = 1;  // elements the strides cover: the same for dense tensors, the parent's for views
+    bool strided = false;    // some tensor is a view into a larger parent
+    bool c_strided = false;  // C is
 };
 
 // A permutation of one caller tensor: dst mode i = src mode perm[i].
@@ -46,6 +49,8 @@ struct TransposeSpec {
     int64_t src_extent[kMaxModes] = {0};
     int perm[kMaxModes] = {0};
     int64_t elements = 0;
+    bool strided_src = false;              // the source is a view: src_stride holds its element strides
+    int64_t src_stride[kMaxModes] = {0};
 };
 
 // How one operand's tile is staged into shared memory for tcgen05.mma: a tile is a run of
@@ -131,6 +136,8 @@ struct CostTable {
     // Least time per stage of the tcgen05 kernel's ring, whatever the stage holds: one pass of the producer's
     // wait-announce-copy sequence (700 to 900 cycles in the main-loop probes).
     double umma_stage_us = 0.45;
+    // What one SM's epilogue stores per second (GB/s): a 128 x 256 fp32 tile takes 3.7 us to leave (cfg4).
+    double umma_store_gbs_per_sm = 35.5;
     int num_sms = 148;  // SMs of the device the plan is made for (api.cpp fills it in from the current device)
 };
 
@@ -141,6 +148,8 @@ struct Plan {
     char op = '?';
     int scalar_type = 1;
     int backend_selection = 0;
+    // Sub-tensor views: extents of each tensor's modes in the parent it is a view of (empty = dense)
+    std::vector<int64_t> parentC, parentA, parentB;
 
     int backend = 0;        // TCONTB_BACKEND_*
     Problem prob;           // what the contraction kernel sees (after the transposes, if any)
@@ -154,9 +163,12 @@ struct Plan {
 };
 
 // Returns 0 (ok), 1 (invalid argument), 3 (unsupported); `err` receives the message.
+// parentC / parentA / parentB (optional): the tensor is a view into a larger column-major tensor whose extents, mode
+// by mode, these are; strides come from them, everything else from the view's extents.
 int make_plan(const char* modeC, int nC, const char* modeA, int nA, const char* modeB, int nB, char op, int scalar_type,
               const char* ext_mode, const int64_t* ext_val, int n_ext, int backend_selection, const CostTable& cost,
-              Plan* plan, std::string* err);
+              Plan* plan, std::string* err, const int64_t* parentC = nullptr, const int64_t* parentA = nullptr,
+              const int64_t* parentB = nullptr);
 
 std::string describe_plan(const Plan& plan);
 // Defaults, overridden by the "key value" file TCONT_COST_TABLE names, if any.

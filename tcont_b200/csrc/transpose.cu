@@ -14,7 +14,7 @@
 
 namespace tcontb {
 
-bool make_transpose_params(int rank, const int64_t* src_extent, const int* perm, TransposeParams* out)
+bool make_transpose_params(int rank, const int64_t* src_extent, const int* perm, TransposeParams* out, const int64_t* src_stride)
 {
     if (rank < 1 || rank > kMaxModes) return false;
     bool seen[kMaxModes] = {false};
@@ -31,19 +31,24 @@ bool make_transpose_params(int rank, const int64_t* src_extent, const int* perm,
     // Merge source modes j, j+1 that are also neighbours (same order) in the destination.
     int pos_in_dst[kMaxModes];
     for (int i = 0; i < rank; ++i) pos_in_dst[perm[i]] = i;
+    // (the source may be a view into a larger tensor: its strides are then given, and two modes merge only
+    // when the second also follows the first in the source's memory)
     int n = 0;
-    int64_t st = 1;
+    int64_t st = 1, dense = 1;
     for (int j = 0; j < rank; ++j) {
-        if (n > 0 && pos_in_dst[j] == pos_in_dst[j - 1] + 1) {
+        const int64_t sj = src_stride ? src_stride[j] : dense;
+        if (n > 0 && pos_in_dst[j] == pos_in_dst[j - 1] + 1 && sj == out->src_stride[n - 1] * out->ext[n - 1]) {
             out->ext[n - 1] *= src_extent[j];
         } else {
             out->ext[n] = src_extent[j];
-            out->src_stride[n] = st;
+            out->src_stride[n] = sj;
             out->dst_stride[n] = dst_stride_of_src[j];
             ++n;
         }
         st *= src_extent[j];
+        dense *= src_extent[j];
     }
+    if (n > 0 && out->src_stride[0] != 1) return false;   // the kernels copy along a contiguous first mode
     out->rank = n;
     out->elements = st;
     return true;
@@ -189,7 +194,9 @@ cudaError_t launch_typed(const T* src, T* dst, const TransposeParams& p, cudaStr
     for (int i = 0; i < p.rank; ++i)
         if (p.dst_stride[i] == 1) d0 = i;
     if (d0 == 0) {
-        const bool vec = aligned && p.ext[0] % VMAX == 0;
+        bool strides_ok = true;   // (a view's rows must start on 16-byte boundaries for the vector loads)
+        for (int i = 1; i < p.rank; ++i) strides_ok = strides_ok && p.src_stride[i] % VMAX == 0;
+        const bool vec = aligned && strides_ok && p.ext[0] % VMAX == 0;
         const int64_t total = p.elements / (vec ? VMAX : 1);
         int dev = 0, sms = 148;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -209,7 +216,9 @@ cudaError_t launch_typed(const T* src, T* dst, const TransposeParams& p, cudaStr
     for (int i = 1; i < p.rank; ++i)
         if (i != d0) blocks *= p.ext[i];
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
-    const bool vec = aligned && p.ext[0] % VMAX == 0 && p.ext[d0] % VMAX == 0;
+    bool strides_ok = true;
+    for (int i = 1; i < p.rank; ++i) strides_ok = strides_ok && p.src_stride[i] % VMAX == 0;
+    const bool vec = aligned && strides_ok && p.ext[0] % VMAX == 0 && p.ext[d0] % VMAX == 0;
     if (vec) permute_tiled_kernel<T, VMAX><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, dst, p, g);
     else permute_tiled_kernel<T, 1><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, dst, p, g);
     return cudaGetLastError();

@@ -214,3 +214,26 @@ def test_planning_is_reentrant(engine):
     for t in threads:
         t.join()
     assert not failures, failures[:3]
+
+
+def test_sub_tensor_views_take_their_strides_from_the_parent(engine):
+    """tcontb_plan_create_strided: modes fuse only where the view leaves no gap between them; a view whose strides
+    are not multiples of 16 bytes cannot be staged by TMA; parents must cover their views."""
+    c = CONFIGS["cfg3"][0]
+    eq = to_equation(engine, c)
+    dense = engine.plan(eq).describe()
+    assert dense["views"] is False and dense["A"] == ["a:48", "e:48", "ij:576"]
+    # A is a view with a gap after i (parent 26 wide in i): i and j no longer fuse anywhere; b and c still do
+    d = engine.plan_views(eq, None, [48, 48, 26, 24], None).describe()
+    assert d["views"] is True and d["A"] == ["a:48", "e:48", "i:24", "j:24"] and d["B"][0] == "bc:2304"
+    assert d["C"] == ["a:48", "bc:2304", "i:24", "j:24", "k:24"]
+    assert d["kernel"] == "dmma_f64_tma"                      # strides stay multiples of 16 bytes
+    # a parent that is one element wider in the stride-1 mode: 8-byte-aligned rows only, so no TMA
+    d = engine.plan_views(eq, None, [49, 48, 24, 24], None).describe()
+    assert d["kernel"] in ("dmma_f64", "simt") and "16 bytes" in d["umma"]["why_not"]
+    # C as a view: no split-K (there is no workspace laid out like C)
+    lk = Contraction("ab", "acd", "dbc", dict(a=312, b=296, c=296, d=312), 1)
+    assert engine.plan(to_equation(engine, lk, 1)).describe()["umma"]["k_splits"] > 1
+    assert engine.plan_views(to_equation(engine, lk, 1), [320, 296], None, None).describe()["umma"]["k_splits"] == 1
+    with pytest.raises(ValueError):
+        engine.plan_views(eq, None, [40, 48, 24, 24], None)   # parent smaller than the view
