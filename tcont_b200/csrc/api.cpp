@@ -139,6 +139,9 @@ struct tcontb_run {
     bool has_host = false;
     // transpose scratch for role A / role B
     DeviceBuffer tbufA, tbufB;
+    // A part of a pipelined host-buffer pass may use the transposed copy another part makes of the operand all
+    // parts share (borrowed_tA / borrowed_tB: that part's scratch; this run then neither allocates nor transposes).
+    const void *borrowed_tA = nullptr, *borrowed_tB = nullptr;
     TransposeParams tpA{}, tpB{};
     // SIMT tables
     DeviceBuffer tables;
@@ -199,6 +202,10 @@ struct tcontb_run {
         bool tried = false;
         bool in_left = false;  // the caller's left operand carries the cut mode
         size_t slice_in = 0, slice_out = 0;  // bytes per part
+        // The cut mode is not the slowest mode of the operand that carries it: a part's slice of that operand is
+        // `rows` pieces of `width` bytes, `pitch` bytes apart (uploaded by a 2-D copy; the part's plan sees a view).
+        bool strided = false;
+        size_t width = 0, pitch = 0, rows = 0;
         std::vector<std::unique_ptr<tcontb_run>> parts;
         cudaStream_t s_in = nullptr, s_out = nullptr;
         cudaEvent_t ev_start = nullptr, ev_other = nullptr;
@@ -317,14 +324,18 @@ tcontb_status finish_run(tcontb_run* run)
     const void* kA = run->roleA_src();
     const void* kB = run->roleB_src();
     run->kernels_per_launch = 1;
-    if (pl.tA.needed) {
+    if (pl.tA.needed && run->borrowed_tA) {
+        kA = run->borrowed_tA;
+    } else if (pl.tA.needed) {
         if (!make_transpose_params(pl.tA.rank, pl.tA.src_extent, pl.tA.perm, &run->tpA, pl.tA.strided_src ? pl.tA.src_stride : nullptr))
             return fail(TCONTB_RUNTIME_ERROR, "bad transpose plan for A");
         TC_CUDA(run->tbufA.alloc(static_cast<size_t>(pl.tA.elements) * run->elt));
         kA = run->tbufA.ptr;
         run->kernels_per_launch++;
     }
-    if (pl.tB.needed) {
+    if (pl.tB.needed && run->borrowed_tB) {
+        kB = run->borrowed_tB;
+    } else if (pl.tB.needed) {
         if (!make_transpose_params(pl.tB.rank, pl.tB.src_extent, pl.tB.perm, &run->tpB, pl.tB.strided_src ? pl.tB.src_stride : nullptr))
             return fail(TCONTB_RUNTIME_ERROR, "bad transpose plan for B");
         TC_CUDA(run->tbufB.alloc(static_cast<size_t>(pl.tB.elements) * run->elt));
@@ -651,8 +662,21 @@ tcontb_status build_host_pipeline(tcontb_run* run)
     const bool left = pl.modeA.find(mode) != std::string::npos, right = pl.modeB.find(mode) != std::string::npos;
     if (left == right) return TCONTB_OK;
     const std::string& carrier = left ? pl.modeA : pl.modeB;
-    if (carrier.back() != mode) return TCONTB_OK;
     const int64_t ext = pl.ext_val[pl.ext_mode.find(mode)];
+    // Where the cut mode is not the carrier's slowest mode, a part's slice of the carrier is a sub-tensor view:
+    // `rows` pieces (one per index of the modes behind the cut mode) of `width` bytes each, `pitch` bytes apart.
+    const bool strided = carrier.back() != mode;
+    std::vector<int64_t> carrier_parent;
+    int64_t inner = 1, outer = 1;
+    {
+        const size_t pos = carrier.find(mode);
+        for (size_t i = 0; i < carrier.size(); ++i) {
+            const int64_t e = pl.ext_val[pl.ext_mode.find(carrier[i])];
+            carrier_parent.push_back(e);
+            if (i < pos) inner *= e;
+            else if (i > pos) outer *= e;
+        }
+    }
     const size_t in_bytes = static_cast<size_t>(left ? pl.sizeL : pl.sizeR) * run->elt, out_bytes = static_cast<size_t>(pl.sizeC) * run->elt;
     int64_t n = 0;
     if (const char* e = std::getenv("TCONT_HOST_CHUNKS")) {
@@ -667,7 +691,11 @@ tcontb_status build_host_pipeline(tcontb_run* run)
     }
     pp.slice_in = in_bytes / static_cast<size_t>(n);
     pp.slice_out = out_bytes / static_cast<size_t>(n);
-    if (pp.slice_in % 16 || pp.slice_out % 16) return TCONTB_OK;
+    pp.strided = strided;
+    pp.width = static_cast<size_t>(inner * (ext / n)) * run->elt;
+    pp.pitch = static_cast<size_t>(inner * ext) * run->elt;
+    pp.rows = static_cast<size_t>(outer);
+    if (pp.slice_in % 16 || pp.slice_out % 16 || (strided && pp.width % 16)) return TCONTB_OK;
     std::vector<int64_t> local_ext = pl.ext_val;
     local_ext[pl.ext_mode.find(mode)] = ext / n;
     std::vector<std::unique_ptr<tcontb_run>> parts;
@@ -677,14 +705,23 @@ tcontb_status build_host_pipeline(tcontb_run* run)
         const int rc = make_plan(pl.modeC.data(), static_cast<int>(pl.modeC.size()), pl.modeA.data(), static_cast<int>(pl.modeA.size()),
                                  pl.modeB.data(), static_cast<int>(pl.modeB.size()), pl.op, pl.scalar_type, pl.ext_mode.data(),
                                  local_ext.data(), static_cast<int>(local_ext.size()), pl.backend_selection, device_cost_table(),
-                                 &part->plan, &err);
+                                 &part->plan, &err, nullptr, strided && left ? carrier_parent.data() : nullptr,
+                                 strided && !left ? carrier_parent.data() : nullptr);
         if (rc) return fail(static_cast<tcontb_status>(rc), err);
         part->elt = run->elt;
         part->stream = run->stream;
-        unsigned char* in = static_cast<unsigned char*>(left ? run->dL : run->dR) + static_cast<size_t>(i) * pp.slice_in;
+        // contiguous slices lie one after the other; a view starts (i * ext / n) indices of the cut mode into the carrier
+        const size_t in_offset = strided ? static_cast<size_t>(i) * pp.width : static_cast<size_t>(i) * pp.slice_in;
+        unsigned char* in = static_cast<unsigned char*>(left ? run->dL : run->dR) + in_offset;
         part->dL = left ? static_cast<void*>(in) : run->dL;
         part->dR = left ? run->dR : static_cast<void*>(in);
         part->dC = static_cast<unsigned char*>(run->dC) + static_cast<size_t>(i) * pp.slice_out;
+        // the operand every part shares is transposed once, by the first part; the others read its copy
+        if (!parts.empty()) {
+            const bool carrier_is_role_a = part->plan.prob.swapped ? !left : left;
+            if (carrier_is_role_a && part->plan.tB.needed && parts[0]->plan.tB.needed) part->borrowed_tB = parts[0]->tbufB.ptr;
+            if (!carrier_is_role_a && part->plan.tA.needed && parts[0]->plan.tA.needed) part->borrowed_tA = parts[0]->tbufA.ptr;
+        }
         const tcontb_status st = finish_run(part.get());
         if (st != TCONTB_OK) return st;
         parts.push_back(std::move(part));
@@ -947,9 +984,9 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
         simt.C = run->scaled_ws.ptr;
     }
     if (t) TC_CUDA(cudaEventRecord(run->ev[0], run->stream));
-    if (pl.tA.needed) TC_CUDA(launch_transpose(run->roleA_src(), run->tbufA.ptr, run->tpA, static_cast<int>(run->elt), run->stream));
+    if (pl.tA.needed && !run->borrowed_tA) TC_CUDA(launch_transpose(run->roleA_src(), run->tbufA.ptr, run->tpA, static_cast<int>(run->elt), run->stream));
     if (t) TC_CUDA(cudaEventRecord(run->ev[1], run->stream));
-    if (pl.tB.needed) TC_CUDA(launch_transpose(run->roleB_src(), run->tbufB.ptr, run->tpB, static_cast<int>(run->elt), run->stream));
+    if (pl.tB.needed && !run->borrowed_tB) TC_CUDA(launch_transpose(run->roleB_src(), run->tbufB.ptr, run->tpB, static_cast<int>(run->elt), run->stream));
     if (t) TC_CUDA(cudaEventRecord(run->ev[2], run->stream));
     if (pl.kernel == KERNEL_UMMA_TF32 && run->tf32x3) {
         TC_CUDA(launch_tf32_residual(static_cast<const float*>(run->kernA), static_cast<float*>(run->loA.ptr), run->kernA_elements, run->stream));
@@ -1148,7 +1185,11 @@ tcontb_status tcontb_run_contract_host(tcontb_run* run, const void* a_host, cons
         else TC_CUDA(cudaMemcpyAsync(run->dL, a_host, static_cast<size_t>(pl.sizeL) * run->elt, cudaMemcpyHostToDevice, pp.s_in));
         TC_CUDA(cudaEventRecord(pp.ev_other, pp.s_in));
         for (size_t i = 0; i < n; ++i) {
-            TC_CUDA(cudaMemcpyAsync(cut_dev + i * pp.slice_in, cut_host + i * pp.slice_in, pp.slice_in, cudaMemcpyHostToDevice, pp.s_in));
+            if (pp.strided)
+                TC_CUDA(cudaMemcpy2DAsync(cut_dev + i * pp.width, pp.pitch, cut_host + i * pp.width, pp.pitch, pp.width, pp.rows,
+                                          cudaMemcpyHostToDevice, pp.s_in));
+            else
+                TC_CUDA(cudaMemcpyAsync(cut_dev + i * pp.slice_in, cut_host + i * pp.slice_in, pp.slice_in, cudaMemcpyHostToDevice, pp.s_in));
             TC_CUDA(cudaEventRecord(pp.ev_in[i], pp.s_in));
         }
         TC_CUDA(cudaStreamWaitEvent(run->stream, pp.ev_other, 0));

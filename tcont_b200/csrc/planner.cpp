@@ -677,6 +677,9 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
     }
     u->raster_group = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(u->tiles_m,
                       std::llround(std::sqrt(double(cost.num_sms) * u->BN / u->BM)))));
+    // Tuning switch: TCONT_UMMA_RASTER=<g> sets the number of tile rows (pair rows for CTA pairs) swept together.
+    if (const char* e = std::getenv("TCONT_UMMA_RASTER"))
+        u->raster_group = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(u->tiles_m, std::atoll(e))));
     // fused row modes: digit 0 carries no C stride of its own, the kernel splits the position (slab_elem_offset)
     for (int which = 0; which < 2; ++which) {
         UmmaOperand& o = which == 0 ? u->a : u->b;

@@ -53,3 +53,17 @@ def test_no_cpu_fallback(engine):
     p = engine.plan(engine.TCEquation("ab", "ak", "kb", dict(a=4, b=4, k=4)))
     with pytest.raises(engine.TcontError, match="no usable CUDA device"):
         engine.prepare(p)
+
+
+def test_status_codes_map_like_the_cpp_surface(engine):
+    """TCONTB_INVALID_ARGUMENT -> std::invalid_argument (ValueError here), TCONTB_RUNTIME_ERROR -> std::runtime_error
+    (TcontError here: what a raised device status word turns a result call into), TCONTB_UNSUPPORTED -> its own
+    exception here, std::runtime_error in the C++ surface (tcont_shim.cpp: everything but invalid_argument)."""
+    from tcont_b200 import api
+    api._check(0)
+    with pytest.raises(ValueError):
+        api._check(1)
+    with pytest.raises(api.TcontError):
+        api._check(2)
+    with pytest.raises(NotImplementedError):
+        api._check(3)

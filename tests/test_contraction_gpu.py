@@ -429,8 +429,11 @@ def test_generated_inputs_roundtrip(engine, oracle, monkeypatch):
 @pytest.mark.parametrize("c", [
     Contraction("abc", "adc", "db", dict(a=64, c=4, b=96, d=64), F32),          # C's slowest mode c is A's slowest: pipelined in parts
     Contraction("abcd", "ea", "ebcd", dict(a=40, b=6, c=5, d=8, e=24), F64),    # ... d is the right operand's slowest mode
-    Contraction("abcde", "efba", "cfd", dict(a=12, b=8, c=16, d=6, e=8, f=8), F32),  # e is A's stride-1 mode: one pass
-], ids=["left", "right", "strided"])
+    Contraction("abcde", "efba", "cfd", dict(a=12, b=8, c=16, d=6, e=8, f=8), F32),  # e is A's stride-1 mode: slices of 4 are views (16-byte pieces), of 2 not possible
+    Contraction("abcd", "aebf", "cfde", dict(a=64, b=4, c=64, d=8, e=6, f=16), F32),  # d is a middle mode of B: every part reads a view of B, uploaded by a 2-D copy;
+                                                                                      # A is transposed once, by the first part
+    Contraction("abcd", "aebf", "cfde", dict(a=24, b=4, c=24, d=8, e=6, f=16), F64),
+], ids=["left", "right", "strided", "view_of_right", "view_of_right_f64"])
 def test_host_buffer_path(engine, oracle, monkeypatch, c, chunks):
     """tcontb_run_contract_host: upload, contraction and download, cut into overlapping parts where slices are contiguous."""
     monkeypatch.setenv("TCONT_HOST_CHUNKS", chunks)
