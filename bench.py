@@ -50,7 +50,7 @@ WORKLOADS = {
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) as captured with ncu
 # on one GPU and summarised in the named file under profiles/; not measured by this run.
 NCU_TRAFFIC = {
-    "cfg5": (48.45e9, "profiles/umma_tf32_kernel_cfg5_full_dram.md"),
+    "cfg5": (22.12e9, "profiles/umma_tf32_kernel_cfg5_full_dram.md"),
     "cfg2": (507.6e6, "profiles/umma_tf32_kernel_cfg2.md"),
     "cfg4": (964.4e6, "profiles/umma_tf32_kernel_cfg4.md"),
     "cfg3": (6 * (1980.4e6 + 53.7e6), "profiles/dmma_tma_kernel_cfg3.md (k=4 capture scaled by the tile count)"),

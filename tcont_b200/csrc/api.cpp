@@ -159,6 +159,8 @@ struct tcontb_run {
     const void *kernA = nullptr, *kernB = nullptr;
     int64_t kernA_elements = 0, kernB_elements = 0;
     DeviceBuffer prof;  // cycle counters of the tcgen05 kernel, only with TCONT_UMMA_PROF=1
+    DeviceBuffer pace;  // progress counters of the tcgen05 kernel's pace keeping (see UmmaParams)
+    size_t pace_bytes = 0;
     // C = alpha * (A*B) + beta * C (tcontb_run_set_scalars); the reference's semantics are alpha 1, beta 0.
     // With other values the contraction writes a workspace and the partial-sum pass applies the scalars.
     double alpha = 1.0, beta = 0.0;
@@ -240,8 +242,9 @@ struct tcontb_run {
                                  n, s[0] / n, s[1] / n, s[2] / n, s[3] / n, s[4] / n, s[5] / n);
                 else if (n)
                     std::fprintf(stderr, "[tcontb prof] ctas=%d mma_total=%.0f mma_wait_acc_empty=%.0f mma_wait_stage_full=%.0f "
-                                 "producer_wait_stage_empty=%.0f epilogue_total=%.0f epilogue_wait_acc_full=%.0f (cycles, mean per CTA; MMA figures over issuing CTAs)\n",
-                                 n, s[0] / n, s[1] / n, s[2] / n, s[3] / n, s[4] / n, s[5] / n);
+                                 "producer_wait_stage_empty=%.0f epilogue_total=%.0f epilogue_wait_acc_full=%.0f pace_cycles=%.0f pace_waits_x2=%.1f "
+                                 "(cycles, mean per CTA; MMA figures over issuing CTAs)\n",
+                                 n, s[0] / n, s[1] / n, s[2] / n, s[3] / n, s[4] / n, s[5] / n, s[6] / n, s[7] / n);
             }
         }
         for (auto& e : ev)
@@ -398,6 +401,29 @@ tcontb_status finish_run(tcontb_run* run)
                 TC_CUDA(run->prof.alloc(static_cast<size_t>(run->num_sms) * 8 * sizeof(long long)));
                 TC_CUDA(cudaMemset(run->prof.ptr, 0, static_cast<size_t>(run->num_sms) * 8 * sizeof(long long)));
                 run->umma.prof = static_cast<long long*>(run->prof.ptr);
+            }
+        }
+        run->umma.pace = nullptr;
+        if (pl.kernel == KERNEL_UMMA_TF32) {
+            // Pace keeping pays where the CTAs walk long panels that do not fit into L2 together: a full grid with
+            // several work units each, 32 or more k iterations per unit, operands of 64 MB or more (the large 4-D
+            // configuration: 28 -> 21 GB read from DRAM per launch, 2 to 4 % less time; on another GPU 47 GB without).
+            // TCONT_UMMA_PACE=0/1 overrides the rule; lead and block size: TCONT_UMMA_PACE_LEAD / _SHIFT.
+            const int64_t units = (u.pair ? (u.tiles_m + 1) / 2 : u.tiles_m) * u.tiles_n * u.k_splits;
+            const int64_t ctas = std::max<int64_t>(1, std::min<int64_t>(units, u.pair ? run->num_sms / 2 : run->num_sms));
+            const int64_t a_elems = pl.tA.needed ? pl.tA.elements : (p.swapped ? pl.sizeR : pl.sizeL);
+            const int64_t b_elems = pl.tB.needed ? pl.tB.elements : (p.swapped ? pl.sizeL : pl.sizeR);
+            bool pace = units >= 2 * ctas && u.k_iters_per_split >= 32 && (a_elems + b_elems) * static_cast<int64_t>(run->elt) >= (64ll << 20);
+            if (const char* pe = std::getenv("TCONT_UMMA_PACE")) pace = pe[0] == '1';
+            if (pace) {
+                const char* le = std::getenv("TCONT_UMMA_PACE_LEAD");
+                const char* se = std::getenv("TCONT_UMMA_PACE_SHIFT");
+                run->umma.pace_lead = le ? std::max(1, std::atoi(le)) : 2;
+                run->umma.pace_shift = se ? std::min(10, std::max(0, std::atoi(se))) : 4;
+                const int64_t iters = ((units + ctas - 1) / ctas) * (u.k_iters_per_split + 1);
+                run->pace_bytes = static_cast<size_t>((iters >> run->umma.pace_shift) + 4) * sizeof(unsigned int);
+                TC_CUDA(run->pace.alloc(run->pace_bytes));
+                run->umma.pace = static_cast<unsigned int*>(run->pace.ptr);
             }
         }
         tcontb_status st = encode_map(u.a, kA, u.elt, &run->tmA);
@@ -995,6 +1021,7 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
         for (int pass = 0; pass < 3; ++pass) {
             UmmaParams q = umma;
             q.C = static_cast<float*>(run->splitk.ptr) + static_cast<long long>(pass) * pl.umma.k_splits * pl.sizeC;
+            if (q.pace) TC_CUDA(cudaMemsetAsync(q.pace, 0, run->pace_bytes, run->stream));   // (a copy-engine node, not a kernel)
             TC_CUDA(launch_umma_tf32(q, maps[pass][0], maps[pass][1], pl.umma.smem_bytes, run->num_sms, run->stream));
         }
     } else if (pl.kernel == KERNEL_UMMA_TF32) {
@@ -1013,6 +1040,7 @@ tcontb_status tcontb_run_launch(tcontb_run* run)
             ks.last_set = ks.set;
             ks.set ^= 1;
         }
+        if (umma.pace) TC_CUDA(cudaMemsetAsync(umma.pace, 0, run->pace_bytes, run->stream));
         TC_CUDA(launch_umma_tf32(umma, &run->tmA, &run->tmB, pl.umma.smem_bytes, run->num_sms, run->stream));
     }
     else if (pl.kernel == KERNEL_DMMA_F64_TMA)

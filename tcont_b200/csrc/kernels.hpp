@@ -88,6 +88,13 @@ struct UmmaParams {
     // owner_base[o][i].  owners = 0 or 1: everything goes to C.  `tn_rotate` shifts the order in which a GPU
     // visits the tile columns, so that the GPUs of a job write to different owners at any one time.
     int store_across_slabs;  // FP64 kernel: see UmmaSpec
+    // tcgen05 kernel, pace keeping: the CTAs (pairs) of a launch walk their panels along k at about the same
+    // pace, so that a panel one of them fetched is still in L2 when the others of its tile row or column ask for
+    // it.  pace[0] counts the producers that have ended, pace[1 + g] those that have started their block g of
+    // 2^pace_shift k iterations; a producer starts block g only when all have started block g - pace_lead
+    // (bounded wait; after one time-out it stops looking).  Zeroed before every launch.  nullptr = off.
+    unsigned int* pace;
+    int pace_shift, pace_lead;
     int owners, tn_per_owner, tn_rotate;
     float* owner_base[kMaxOwners];
 };

@@ -37,6 +37,17 @@ __device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const void* tmap,
         : "memory");
 }
 
+__device__ __forceinline__ void red_add_relaxed(unsigned int* addr, unsigned int v)
+{
+    asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_relaxed(const unsigned int* addr)
+{
+    unsigned int v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+
 // Address of the same shared-memory location in CTA `rank` of the cluster.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank)
 {
@@ -218,6 +229,11 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         uint32_t issued_mask = 0, issued_parity = 0;
         long long t_empty = 0;
         int cta_iter = 0;  // k iterations this CTA has gone through (test hook: one of them may be left out)
+        // pace keeping (see UmmaParams): one producer per work unit takes part
+        const bool pacing = p.pace != nullptr && rank == 0;
+        bool pace_live = pacing;
+        const unsigned int pace_peers = PAIR ? gridDim.x / 2u : gridDim.x;
+        long long pace_waits = 0, pace_clk = 0;
         // One look at the next stage's empty barrier is issued right behind the copies of the current one, so
         // that its latency overlaps theirs; `have_slot` says that look found the stage free.
         bool have_slot = false;
@@ -254,6 +270,25 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             int kd0 = w.it0 % p.k_digit_ext[0], kd1 = (w.it0 / p.k_digit_ext[0]) % p.k_digit_ext[1];
             int kd2 = w.it0 / (p.k_digit_ext[0] * p.k_digit_ext[1]);
             for (int it = 0; it < w.n_it; ++it, ++cta_iter) {
+                if (pace_live && (cta_iter & ((1 << p.pace_shift) - 1)) == 0) {
+                    const int blk = cta_iter >> p.pace_shift;
+                    int go = 1;
+                    if (lane == 0) {
+                        red_add_relaxed(p.pace + 1 + blk, 1u);
+                        if (blk >= p.pace_lead) {
+                            const long long tp = p.prof ? clock64() : 0;
+                            const unsigned int* behind = p.pace + 1 + blk - p.pace_lead;
+                            unsigned long long t_start = 0;
+                            while (ld_relaxed(behind) + ld_relaxed(p.pace) < pace_peers) {
+                                const unsigned long long now = global_timer();
+                                if (t_start == 0) { t_start = now; ++pace_waits; }
+                                else if (now - t_start > 50000ull) { go = 0; break; }   // 50 us: somebody is not running; stop keeping pace
+                            }
+                            if (p.prof) pace_clk += clock64() - tp;
+                        }
+                    }
+                    pace_live = __shfl_sync(0xffffffffu, go, 0) != 0;
+                }
                 const long long t0 = p.prof ? clock64() : 0;
                 const bool ok = have_slot || __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + stage), phase ^ 1u, abort_flag, 0, p.wait_limit_ns));
                 if (p.prof) t_empty += clock64() - t0;
@@ -292,7 +327,12 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                 have_slot = __all_sync(0xffffffffu, mbar_test_wait(smem_u32(bar_empty + stage), phase ^ 1u));
             }
         }
-        if (p.prof && lane == 0) p.prof[blockIdx.x * 8 + 3] = t_empty;
+        if (pacing && lane == 0) red_add_relaxed(p.pace, 1u);
+        if (p.prof && lane == 0) {
+            p.prof[blockIdx.x * 8 + 3] = t_empty;
+            p.prof[blockIdx.x * 8 + 6] = pace_clk;
+            p.prof[blockIdx.x * 8 + 7] = pace_waits * 2 + (pacing && !pace_live ? 1 : 0);
+        }
         if (ld_shared_u32(abort_flag) && lane == 0 && rank == 0) {
             // Give the bulk copies issued into this barrier a bounded time to land before the CTA ends.
             for (int s = 0; s < p.stages; ++s) {

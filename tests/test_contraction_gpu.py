@@ -529,6 +529,24 @@ def test_cta_pairs_with_k_chunks_of_64(engine, oracle, monkeypatch, name):
     check(oracle, c, A, B, out, desc)
 
 
+@pytest.mark.parametrize("pair", ["0", "1"])
+@pytest.mark.parametrize("lead,shift", [("2", "4"), ("1", "0")])
+def test_pace_keeping_changes_no_result(engine, oracle, monkeypatch, pair, lead, shift):
+    """The tcgen05 kernel's producers keep one another's pace along k on large problems (a progress counter per
+    block of k iterations, bounded waits).  Forced on here, on a problem with several work units per CTA and many
+    k iterations, with the default setting and with a check on every iteration: same results, twice in a row
+    (the counters are zeroed before every launch)."""
+    monkeypatch.setenv("TCONT_UMMA_PACE", "1")
+    monkeypatch.setenv("TCONT_UMMA_PACE_LEAD", lead)
+    monkeypatch.setenv("TCONT_UMMA_PACE_SHIFT", shift)
+    monkeypatch.setenv("TCONT_UMMA_PAIR", pair)
+    c = Contraction("abc", "adc", "db", dict(a=256, c=18, b=2048, d=800), F32)
+    A, B = oracle.inputs(c, 67, -1.0, 1.0)
+    out, desc = run_contraction(engine, c, A, B, 1, launches=2)
+    assert desc["kernel"] == "umma_tf32" and desc["umma"]["pair"] is (pair == "1"), desc["umma"]
+    check(oracle, c, A, B, out, desc)
+
+
 ACROSS_SLABS_SHAPES = {
     # FP64, A MN-major on a mode that is not C's stride-1 mode (reference cases 3, 4, 6-8 and 1): tiles of
     # 16 elements of A's stride-1 mode x 8 indices of C's stride-1 mode, stored across slabs
