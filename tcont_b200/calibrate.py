@@ -98,21 +98,24 @@ def calibrate() -> dict:
     # far-row penalty: the same 4-D contraction with A where the large configuration has it (the k rows of a TMA box
     # 8 MB apart, every one in another 2 MB page: half of the bytes a CTA of a pair stages) and with A already in the
     # layout the transpose-assisted route gives it (rows 512 bytes apart): rate_far = rate_near * (1 - p / 2)
-    ext = dict(a=128, b=128, c=128, d=128, e=128, f=32)
+    # (f = 64: the contracted mode that is cut into chunks must be long enough for the kernel form the large
+    # configuration runs on, CTA pairs with a k chunk of 64; on the one-CTA form with chunks of 32 the two layouts
+    # differ by 3 to 8 %, on pairs by a quarter)
+    ext = dict(a=128, b=128, c=128, d=128, e=128, f=64)
     far, _ = _rate(tc, api, torch, ("abcd", "aebf", "cfde"), ext, F32, iters=3)
     near, _ = _rate(tc, api, torch, ("abcd", "afeb", "cfde"), ext, F32, iters=3)
     table["far_row_penalty"] = max(0.0, min(1.0, 2.0 * (1.0 - far / max(near, 1e-9))))
-    # what one more kernel costs in a chain of back-to-back launches: a permutation too small to matter
-    tiny = torch.zeros(4096, device="cuda", dtype=torch.float32)
-    tiny2 = torch.zeros_like(tiny)
-    for _ in range(20):
-        api.transpose(tiny.data_ptr(), tiny2.data_ptr(), [64, 64], [1, 0], 4, stream)
-    e0.record()
-    for _ in range(500):
-        api.transpose(tiny.data_ptr(), tiny2.data_ptr(), [64, 64], [1, 0], 4, stream)
-    e1.record()
-    torch.cuda.synchronize()
-    table["launch_us"] = e0.elapsed_time(e1) / 500 * 1e3
+    # what one more kernel costs in a chain of back-to-back launches: a contraction too small to matter, launched in
+    # a loop inside the library (a loop in Python would measure the interpreter)
+    eq = tc.TCEquation("ab", "ak", "kb", dict(a=16, b=16, k=16), "-", F32, tc.BackendSelection.COGENT)
+    plan = tc.plan(eq)
+    ta = torch.zeros(256, device="cuda", dtype=torch.float32)
+    tb = torch.zeros(256, device="cuda", dtype=torch.float32)
+    tcc = torch.zeros(256, device="cuda", dtype=torch.float32)
+    run = api.prepare_on_device(plan, ta.data_ptr(), tb.data_ptr(), tcc.data_ptr(), keep=(ta, tb, tcc))
+    tc.warmup(run, 20)
+    ms, _ = run.time_launches(2000)
+    table["launch_us"] = ms / 2000 * 1e3
 
     # ---- for the record: rates of the helper kernels (CUDA events; read + write bytes over time) ----
     def permute_gbs(extent, perm, dtype, iters=10):

@@ -118,17 +118,17 @@ struct CostTable {
     // Defaults: what `python -m tcont_b200.calibrate` measured on a B200 (the file it writes,
     // tcont_cost_table.NVIDIA_B200.txt beside the library, holds the same figures and is read when the current
     // device has that name; TCONT_COST_TABLE names another "key value" file).
-    double hbm_gbs = 6207.9;                // copy through the permutation kernel, read + write
-    double umma_tf32_tflops = 687.9;        // tcgen05 kernel, 8192 x 8192 x 4096, CTA pairs with a k chunk of 64
+    double hbm_gbs = 6186.1;                // copy through the permutation kernel, read + write
+    double umma_tf32_tflops = 682.8;        // tcgen05 kernel, 8192 x 8192 x 4096, CTA pairs with a k chunk of 64
     double simt_f32_tflops = 23.7;
     double simt_f64_tflops = 16.4;
-    double dmma_f64_tflops = 33.4;          // TMA-fed tensor-path kernel
-    double dmma_f64_gather_tflops = 20.9;   // gather tensor-path kernel, 16-byte gathers
-    double dmma_f64_gather8_tflops = 15.6;  // gather tensor-path kernel, an operand on 8-byte gathers
+    double dmma_f64_tflops = 33.7;          // TMA-fed tensor-path kernel
+    double dmma_f64_gather_tflops = 20.8;   // gather tensor-path kernel, 16-byte gathers
+    double dmma_f64_gather8_tflops = 15.5;  // gather tensor-path kernel, an operand on 8-byte gathers
     double dmma_f64_gather_narrow_tflops = 6.5;  // gather tensor-path kernel, 256 x 32 tiles (N <= 48)
     double scatter_store_ps = 28.0;         // per element of C stored on its own (TMA-fed FP64 kernel)
-    double scatter_store_f32_ps = 13.3;     // the same for the tcgen05 kernel's 4-byte elements
-    double launch_us = 3.0;                 // one more kernel in a chain of back-to-back launches
+    double scatter_store_f32_ps = 18.6;     // the same for the tcgen05 kernel's 4-byte elements
+    double launch_us = 7.9;                 // one more launch through the library (a contraction too small to matter, in a loop)
     // Fraction of the tcgen05 rate lost per unit of staged bytes whose K rows lie 2 MB or more apart, i.e. every row
     // of a TMA box in another 2 MB page (cfg5 where it lies, A's rows 8 MB apart, half of a pair's bytes: 424 TFLOP/s
     // against 587 after the transpose that brings them together; with rows 1 MB apart there is no loss: 701 / 689).

@@ -42,16 +42,16 @@ def main():
         raise SystemExit("oracle/_ref/bench_tccg is missing (make -C oracle, where the reference tree is available)")
     for precision in (["fp64", "tf32"] if args.precision == "both" else [args.precision]):
         print(f"\n## {precision}\n")
-        print("| case | direct ms | ttgt ms | model ms | model took | faster | right | regret |")
-        print("|---|---|---|---|---|---|---|---|")
+        print("| case | direct ms | ttgt ms | model ms | model GFLOP/s | model took | faster | right | regret |")
+        print("|---|---|---|---|---|---|---|---|---|")
         right = total = 0
         worst = 1.0
         for eq in range(args.start, args.end + 1):
             _, t_direct, _ = run(eq, precision, "cogent")
             took_t, t_ttgt, _ = run(eq, precision, "ttgt")
-            took, t_model, _ = run(eq, precision, "model")
+            took, t_model, gf_model = run(eq, precision, "model")
             if None in (t_direct, t_ttgt, t_model):
-                print(f"| {eq} | error | | | | | | |")
+                print(f"| {eq} | error | | | | | | | |")
                 continue
             # `--backend ttgt` on a case that needs no transpose runs the direct kernel and reports it as such
             same_route = abs(t_direct - t_ttgt) <= 0.03 * min(t_direct, t_ttgt)
@@ -63,7 +63,7 @@ def main():
             total += 1
             right += int(ok)
             worst = max(worst, regret)
-            print(f"| {eq} | {t_direct:.4f} | {t_ttgt:.4f} | {t_model:.4f} | {took} | {faster} | {'yes' if ok else 'no'} | {regret:.3f} |")
+            print(f"| {eq} | {t_direct:.4f} | {t_ttgt:.4f} | {t_model:.4f} | {gf_model:.0f} | {took} | {faster} | {'yes' if ok else 'no'} | {regret:.3f} |")
             sys.stdout.flush()
         if total:
             print(f"\n{precision}: the model took the faster route (or the routes tie within 3 %) in {right} of {total} cases "
