@@ -130,9 +130,10 @@ struct CostTable {
     double scatter_store_f32_ps = 18.6;     // the same for the tcgen05 kernel's 4-byte elements
     double launch_us = 7.9;                 // one more launch through the library (a contraction too small to matter, in a loop)
     // Fraction of the tcgen05 rate lost per unit of staged bytes whose K rows lie 2 MB or more apart, i.e. every row
-    // of a TMA box in another 2 MB page (cfg5 where it lies, A's rows 8 MB apart, half of a pair's bytes: 424 TFLOP/s
-    // against 587 after the transpose that brings them together; with rows 1 MB apart there is no loss: 701 / 689).
-    double far_row_penalty = 0.55;
+    // of a TMA box in another 2 MB page (the calibration probe: the large 4-D configuration with f = 64, A's rows 8 MB
+    // apart, half of a pair's bytes; the configuration itself: 18.7 ms where A lies against 14.1 ms through the
+    // transpose that brings the rows together, i.e. 0.53; with rows 1 MB apart there is no loss: 701 / 689 TFLOP/s).
+    double far_row_penalty = 0.43;
     // Least time per stage of the tcgen05 kernel's ring, whatever the stage holds: one pass of the producer's
     // wait-announce-copy sequence (700 to 900 cycles in the main-loop probes).
     double umma_stage_us = 0.45;

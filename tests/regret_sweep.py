@@ -1,6 +1,7 @@
 """How good is the planner's choice between its two routes?  (Run on a GPU box; not a pytest module.)
 
     python tests/regret_sweep.py [--precision fp64|tf32|both] [--start 1] [--end 48] > regret.md
+    python tests/regret_sweep.py --verified > verified.md     # `--backend model --verify`, cases 12 and 20-30 left out
 
 For every case of the reference's table the reference's own unchanged driver (oracle/_ref/bench_tccg, see
 tests/test_reference_harness_gpu.py) is run three times: `--backend cogent` (direct kernel), `--backend ttgt`
@@ -21,15 +22,39 @@ BENCH = os.path.join(ROOT, "oracle", "_ref", "bench_tccg")
 LINE = re.compile(r"^TCCG_RESULT equation=(\d+) precision=(\w+) backend=(\w+) operations=(\d+) time_ms=([0-9.]+) gflops=([0-9.]+) validation=(\w+)$")
 
 
-def run(equation, precision, backend):
+def run(equation, precision, backend, verify=False):
     env = dict(os.environ)
     env["TCONT_SEED"] = "7"
-    done = subprocess.run([BENCH, "-b", str(equation), f"--{precision}", "--backend", backend], capture_output=True, text=True, env=env, timeout=900)
+    cmd = [BENCH, "-b", str(equation), f"--{precision}", "--backend", backend] + (["--verify"] if verify else [])
+    done = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=1800)
     for line in (done.stdout + done.stderr).splitlines():
         m = LINE.match(line.strip())
         if m and done.returncode == 0:
-            return m.group(3), float(m.group(5)), float(m.group(6))
-    return None, None, None
+            return (m.group(3), float(m.group(5)), float(m.group(6))) + ((m.group(7),) if verify else ())
+    return (None, None, None) + ((None,) if verify else ())
+
+
+def verified_sweep(args):
+    """`--backend model --verify` on every case but those whose CPU loop nest takes minutes (12, 20-30)."""
+    slow = {12} | set(range(20, 31))
+    for precision in (["fp64", "tf32"] if args.precision == "both" else [args.precision]):
+        print(f"\n## {precision}, --backend model --verify\n")
+        print("| case | backend | ms | GFLOP/s | validation |")
+        print("|---|---|---|---|---|")
+        passed = failed = 0
+        for eq in range(args.start, args.end + 1):
+            if eq in slow:
+                continue
+            took, ms, gf, val = run(eq, precision, "model", verify=True)
+            if took is None:
+                print(f"| {eq} | error | | | |")
+                failed += 1
+                continue
+            passed += int(val == "PASS")
+            failed += int(val != "PASS")
+            print(f"| {eq} | {took} | {ms:.4f} | {gf:.0f} | {val} |")
+            sys.stdout.flush()
+        print(f"\n{precision}: {passed} passed, {failed} failed (the reference's own loop nest and comparator).")
 
 
 def main():
@@ -37,9 +62,13 @@ def main():
     ap.add_argument("--precision", default="both", choices=["fp64", "tf32", "both"])
     ap.add_argument("--start", type=int, default=1)
     ap.add_argument("--end", type=int, default=48)
+    ap.add_argument("--verified", action="store_true", help="run `--backend model --verify` instead of the three-way timing")
     args = ap.parse_args()
     if not os.path.exists(BENCH):
         raise SystemExit("oracle/_ref/bench_tccg is missing (make -C oracle, where the reference tree is available)")
+    if args.verified:
+        verified_sweep(args)
+        return
     for precision in (["fp64", "tf32"] if args.precision == "both" else [args.precision]):
         print(f"\n## {precision}\n")
         print("| case | direct ms | ttgt ms | model ms | model GFLOP/s | model took | faster | right | regret |")
