@@ -238,33 +238,51 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         // that its latency overlaps theirs; `have_slot` says that look found the stage free.
         bool have_slot = false;
 
-        for (uint32_t tile = first_unit; tile < total_tiles; tile += unit_step) {
-            const WorkUnit w = decode_unit(tile, p, tiles_m, tiles_n);
-            const uint32_t tm = w.tm, tn = w.tn;
-            int base[kMaxTmaRank] = {0, 0, 0, 0, 0};
-            if (active) {
-                const uint32_t s = is_a ? (PAIR ? 2u * tm + rank : tm) * SA + slab
-                                        : tn * SB + (PAIR ? rank * SBL : 0u) + slab;
-                if (s < static_cast<uint32_t>(o.total_slabs)) {
-                    uint32_t rem = s;
+        // TMA coordinates of this lane's copy for the rows / columns of a work unit (the k coordinates come on top);
+        // worked out one unit ahead, so that the first copies of a unit do not wait for the divisions
+        auto unit_base = [&](const WorkUnit& u, int (&base)[kMaxTmaRank]) {
 #pragma unroll
-                    for (int d = 0; d < kMaxTmaRank; ++d) {
-                        if (d < o.n_row_digits) {
-                            const uint32_t e = static_cast<uint32_t>(o.row_digit_ext[d]);
-                            const int idx = static_cast<int>(rem % e);
-                            rem /= e;
-                            const int v = d == o.chunk_digit ? idx * o.digit0_scale : idx;
+            for (int t = 0; t < kMaxTmaRank; ++t) base[t] = 0;
+            if (!active) return;
+            const uint32_t s = is_a ? (PAIR ? 2u * u.tm + rank : u.tm) * SA + slab
+                                    : u.tn * SB + (PAIR ? rank * SBL : 0u) + slab;
+            if (s < static_cast<uint32_t>(o.total_slabs)) {
+                uint32_t rem = s;
 #pragma unroll
-                            for (int t = 0; t < kMaxTmaRank; ++t)
-                                if (o.row_digit_dim[d] == t) base[t] = v;
-                        }
+                for (int d = 0; d < kMaxTmaRank; ++d) {
+                    if (d < o.n_row_digits) {
+                        const uint32_t e = static_cast<uint32_t>(o.row_digit_ext[d]);
+                        const int idx = static_cast<int>(rem % e);
+                        rem /= e;
+                        const int v = d == o.chunk_digit ? idx * o.digit0_scale : idx;
+#pragma unroll
+                        for (int t = 0; t < kMaxTmaRank; ++t)
+                            if (o.row_digit_dim[d] == t) base[t] = v;
                     }
-                } else {
-                    // Slab beyond the tensor: start the box past the slab mode's end, TMA fills zeros.
-#pragma unroll
-                    for (int t = 0; t < kMaxTmaRank; ++t)
-                        if (o.row_digit_dim[o.chunk_digit] == t) base[t] = o.oob_coord;
                 }
+            } else {
+                // Slab beyond the tensor: start the box past the slab mode's end, TMA fills zeros.
+#pragma unroll
+                for (int t = 0; t < kMaxTmaRank; ++t)
+                    if (o.row_digit_dim[o.chunk_digit] == t) base[t] = o.oob_coord;
+            }
+        };
+        WorkUnit w_next{};
+        int base_next[kMaxTmaRank] = {0, 0, 0, 0, 0};
+        if (first_unit < total_tiles) {
+            w_next = decode_unit(first_unit, p, tiles_m, tiles_n);
+            unit_base(w_next, base_next);
+        }
+
+        for (uint32_t tile = first_unit; tile < total_tiles; tile += unit_step) {
+            const WorkUnit w = w_next;
+            int base[kMaxTmaRank];
+#pragma unroll
+            for (int t = 0; t < kMaxTmaRank; ++t) base[t] = base_next[t];
+            const bool have_next = tile + unit_step < total_tiles;
+            if (have_next) {
+                w_next = decode_unit(tile + unit_step, p, tiles_m, tiles_n);
+                unit_base(w_next, base_next);
             }
             // K digits: chunk of the chunked mode, then the other K modes
             int kd0 = w.it0 % p.k_digit_ext[0], kd1 = (w.it0 / p.k_digit_ext[0]) % p.k_digit_ext[1];
