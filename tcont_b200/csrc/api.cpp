@@ -356,6 +356,7 @@ tcontb_status finish_run(tcontb_run* run)
         run->umma.BK = u.BK;
         run->umma.stages = u.stages;
         run->umma.pair = u.pair ? 1 : 0;
+        run->umma.producers = u.producers;
         run->umma.store_across_slabs = u.store_across_slabs ? 1 : 0;
         run->umma.n_k_digits = u.n_k_digits;
         for (int i = 0; i < 3; ++i) run->umma.k_digit_ext[i] = static_cast<int>(u.k_digit_ext[i]);

@@ -64,6 +64,7 @@ struct UmmaParams {
     UmmaOperandDev a, b;
     int BN, BK, stages, n_k_digits;
     int pair;  // 1: two-CTA clusters, 256 x BN tiles (cta_group::2); 0: one CTA per 128 x BN tile
+    int producers;  // tcgen05 kernel: 2 = two producer warps taking turns stage by stage (needs an even number of stages)
     int k_digit_ext[3];
     int k_iters;
     // Split-K: every tile is computed k_splits times over consecutive ranges of k_iters_per_split

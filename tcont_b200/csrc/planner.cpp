@@ -635,6 +635,12 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
     const int budget = f64 ? 200 * 1024 : 227 * 1024 - 8 * 1024;
     u->stages = std::max(2, std::min(8, budget / stage_bytes));
     if (f64) u->stages &= ~1;  // one ring of stages per consumer group
+    // Tuning switch: TCONT_UMMA_PRODUCERS=2 lets two producer warps take turns (tcgen05 kernel)
+    if (const char* e = std::getenv("TCONT_UMMA_PRODUCERS"))
+        if (!f64 && std::atoi(e) == 2 && u->stages >= 4) {
+            u->producers = 2;
+            u->stages &= ~1;
+        }
     u->smem_bytes = u->stages * stage_bytes + 8 * 1024 + 1024;
     // Split-K: with few waves of tiles and a long contracted extent, cut the k iterations into ranges
     // computed as separate work units (partials summed by a second kernel).  Of the admissible counts
@@ -1121,7 +1127,7 @@ std::string describe_plan(const Plan& pl)
           << ",\"a_slab_w\":" << u.a.slab_w << ",\"b_slab_w\":" << u.b.slab_w << ",\"a_slabs_per_copy\":" << u.a.slabs_per_op << ",\"b_slabs_per_copy\":" << u.b.slabs_per_op << ",\"a_slabs\":" << u.a.slabs_per_tile
           << ",\"b_slabs\":" << u.b.slabs_per_tile << ",\"smem_bytes\":" << u.smem_bytes
           << ",\"coalesced_store\":" << (u.a.row_elem_cstride == 1 ? "true" : "false")
-          << ",\"store_across_slabs\":" << (u.store_across_slabs ? "true" : "false");
+          << ",\"store_across_slabs\":" << (u.store_across_slabs ? "true" : "false") << ",\"producers\":" << u.producers;
     }
     o << "}}";
     return o.str();

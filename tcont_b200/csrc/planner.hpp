@@ -101,6 +101,7 @@ struct UmmaSpec {
     double far_fraction = 0;  // share of a stage's bytes whose K rows are 64 KB or more apart in memory
     int raster_group = 16;
     bool pair = false;  // two-CTA clusters working on 256-row tiles (tcgen05 cta_group::2)
+    int producers = 1;  // tcgen05 kernel: producer warps taking turns stage by stage (2 needs an even number of stages)
     // FP64 kernel: the slabs of an A tile are consecutive indices of C's stride-1 mode (which is not A's stride-1
     // mode); a thread stores the same row of four neighbouring slabs as one 32-byte piece
     bool store_across_slabs = false;

@@ -26,7 +26,7 @@
 namespace tcontb {
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;   // warp 0 producer, 1 MMA issue, 2-5 epilogue, 6 second producer (idle with one producer)
 // The same copy for a CTA pair: the destination is this CTA's shared memory, the mbarrier may live
 // in the partner CTA (address in the cluster window).  No multicast.
 __device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0, int c1, int c2, int c3, int c4)
@@ -209,8 +209,12 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     const uint32_t first_unit = PAIR ? blockIdx.x / 2u : blockIdx.x;
     const uint32_t unit_step = PAIR ? gridDim.x / 2u : gridDim.x;
 
-    if (warp == 0) {
+    if (warp == 0 || (warp == 6 && p.producers == 2)) {
         // ---------------- TMA producer: lane i owns slab i of the stage ----------------
+        // With two producers (p.producers == 2, an even number of stages) warp 0 fills the even k iterations of the
+        // CTA and warp 6 the odd ones: the wait-announce-copy round trip of one warp may then take two stages' worth
+        // of MMA time, which is what lets stages be half as large and the ring twice as deep.
+        const int np = p.producers == 2 ? 2 : 1, pi = warp == 0 ? 0 : 1;
         // lane i owns copy i of the stage; a copy brings slabs_per_op consecutive slabs
         const int OA = SA / p.a.slabs_per_op, OBL = SBL / p.b.slabs_per_op;
         const bool is_a = lane < OA;
@@ -230,7 +234,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
         long long t_empty = 0;
         int cta_iter = 0;  // k iterations this CTA has gone through (test hook: one of them may be left out)
         // pace keeping (see UmmaParams): one producer per work unit takes part
-        const bool pacing = p.pace != nullptr && rank == 0;
+        const bool pacing = p.pace != nullptr && rank == 0 && pi == 0;
         bool pace_live = pacing;
         const unsigned int pace_peers = PAIR ? gridDim.x / 2u : gridDim.x;
         long long pace_waits = 0, pace_clk = 0;
@@ -288,7 +292,8 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
             int kd0 = w.it0 % p.k_digit_ext[0], kd1 = (w.it0 / p.k_digit_ext[0]) % p.k_digit_ext[1];
             int kd2 = w.it0 / (p.k_digit_ext[0] * p.k_digit_ext[1]);
             for (int it = 0; it < w.n_it; ++it, ++cta_iter) {
-                if (pace_live && (cta_iter & ((1 << p.pace_shift) - 1)) == 0) {
+                const bool mine = np == 1 || (cta_iter & 1) == pi;
+                if (mine && pace_live && (cta_iter & ((1 << p.pace_shift) - 1)) == 0) {
                     const int blk = cta_iter >> p.pace_shift;
                     int go = 1;
                     if (lane == 0) {
@@ -308,7 +313,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                     pace_live = __shfl_sync(0xffffffffu, go, 0) != 0;
                 }
                 const long long t0 = p.prof ? clock64() : 0;
-                const bool ok = have_slot || __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + stage), phase ^ 1u, abort_flag, 0, p.wait_limit_ns));
+                const bool ok = mine && (have_slot || __all_sync(0xffffffffu, mbar_wait(smem_u32(bar_empty + stage), phase ^ 1u, abort_flag, 0, p.wait_limit_ns)));
                 if (p.prof) t_empty += clock64() - t0;
                 if (ok && cta_iter != p.test_skip_iter) {
                     // one arrival with the byte count of the whole stage; in a pair the MMA-issuing CTA
@@ -342,11 +347,18 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                     stage = 0;
                     phase ^= 1u;
                 }
-                have_slot = __all_sync(0xffffffffu, mbar_test_wait(smem_u32(bar_empty + stage), phase ^ 1u));
+                // a look at the stage of this warp's next iteration (the next one, or the one after it)
+                if (np == 1) {
+                    have_slot = __all_sync(0xffffffffu, mbar_test_wait(smem_u32(bar_empty + stage), phase ^ 1u));
+                } else if (mine) {
+                    const int s2 = stage + 1 == p.stages ? 0 : stage + 1;
+                    const uint32_t ph2 = stage + 1 == p.stages ? phase ^ 1u : phase;
+                    have_slot = __all_sync(0xffffffffu, mbar_test_wait(smem_u32(bar_empty + s2), ph2 ^ 1u));
+                }
             }
         }
         if (pacing && lane == 0) red_add_relaxed(p.pace, 1u);
-        if (p.prof && lane == 0) {
+        if (p.prof && lane == 0 && pi == 0) {
             p.prof[blockIdx.x * 8 + 3] = t_empty;
             p.prof[blockIdx.x * 8 + 6] = pace_clk;
             p.prof[blockIdx.x * 8 + 7] = pace_waits * 2 + (pacing && !pace_live ? 1 : 0);
@@ -434,7 +446,7 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
                 p.prof[blockIdx.x * 8 + 2] = t_full;
             }
         }
-    } else {
+    } else if (warp < 6) {
         // ---------------- epilogue: 4 warps, warp w reads TMEM lanes 32*(w%4).. ----------------
         const int q = warp & 3;
         const int row = q * 32 + lane;
