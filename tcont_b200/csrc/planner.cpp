@@ -635,12 +635,15 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
     const int budget = f64 ? 200 * 1024 : 227 * 1024 - 8 * 1024;
     u->stages = std::max(2, std::min(8, budget / stage_bytes));
     if (f64) u->stages &= ~1;  // one ring of stages per consumer group
-    // Tuning switch: TCONT_UMMA_PRODUCERS=2 lets two producer warps take turns (tcgen05 kernel)
+    // One CTA per tile (k chunks of up to 32: a stage is at most four MMAs, 512 cycles): two producer warps take
+    // turns stage by stage, because one warp's wait-announce-copy round trip takes 700 to 900 cycles whatever the
+    // stage holds (reference cases 13, 15, 21, 24 in TF32: 1.24 to 1.67 times faster; nothing to gain with one k
+    // iteration per tile).  CTA pairs keep one producer and stages of 64 k (two producers on half-size stages were
+    // measured slower there: 0.297 against 0.248 ms on the 3-D configuration).  TCONT_UMMA_PRODUCERS=1|2 overrides.
+    if (!f64 && !u->pair && u->stages >= 4 && u->k_iters >= 2) u->producers = 2;
     if (const char* e = std::getenv("TCONT_UMMA_PRODUCERS"))
-        if (!f64 && std::atoi(e) == 2 && u->stages >= 4) {
-            u->producers = 2;
-            u->stages &= ~1;
-        }
+        if (!f64) u->producers = std::atoi(e) == 2 && u->stages >= 4 ? 2 : 1;
+    if (u->producers == 2) u->stages &= ~1;
     u->smem_bytes = u->stages * stage_bytes + 8 * 1024 + 1024;
     // Split-K: with few waves of tiles and a long contracted extent, cut the k iterations into ranges
     // computed as separate work units (partials summed by a second kernel).  Of the admissible counts
@@ -661,7 +664,7 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
             const int64_t rounds = ceil_div(units, wave);
             const double eff = double(units) / double(rounds * wave);
             double t = flops / (rate * eff);
-            if (!f64) t = std::max(t, double(rounds) * double(ceil_div(u->k_iters, s)) * cost.umma_stage_us);
+            if (!f64) t = std::max(t, double(rounds) * double(ceil_div(u->k_iters, s)) * cost.umma_stage_us / u->producers);
             return t + (s > 1 ? cost.launch_us + 2.0 * double(s) * double(p.sizeC) * elt / (cost.hbm_gbs * 1e3) : 0.0);
         };
         int64_t splits = 1;
@@ -812,7 +815,7 @@ double contraction_us(const Problem& p, int kernel, const UmmaSpec& u, const Cos
         const int64_t wave = u.pair ? c.num_sms / 2 : c.num_sms;
         // ... and a tile leaves an SM no faster than the epilogue stores it (cfg4: 7 776 tiles of 128 x 256 in 0.196 ms)
         const double tile_store_us = double(u.BM) * double(u.BN) * 4.0 / (c.umma_store_gbs_per_sm * 1e3);
-        extra_floor_us = double(ceil_div(units, wave)) * std::max(double(u.k_iters_per_split) * c.umma_stage_us, tile_store_us);
+        extra_floor_us = double(ceil_div(units, wave)) * std::max(double(u.k_iters_per_split) * c.umma_stage_us / u.producers, tile_store_us);
     }
     const double bytes = (double(p.sizeA) + double(p.sizeB)) * elt + c_bytes;
     // scattered stores are a third ceiling rather than an addition: one consumer group stores while the

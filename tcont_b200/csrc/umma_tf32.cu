@@ -19,6 +19,7 @@
 // kernel_store.py:280-507): same contract (C overwritten with the fp32-accumulated TF32
 // products; raw fp32 bits are handed to the tensor core, which ignores the low mantissa bits).
 #include <cuda.h>
+#include <cstdlib>
 
 #include "kernels.hpp"
 #include "tile_common.cuh"
@@ -26,7 +27,7 @@
 namespace tcontb {
 namespace {
 
-constexpr int kThreads = 224;   // warp 0 producer, 1 MMA issue, 2-5 epilogue, 6 second producer (idle with one producer)
+constexpr int kThreads = 224;   // warp 0 producer, 1 MMA issue, 2-5 epilogue, 6 second producer (launched only with two producers)
 // The same copy for a CTA pair: the destination is this CTA's shared memory, the mbarrier may live
 // in the partner CTA (address in the cluster window).  No multicast.
 __device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0, int c1, int c2, int c3, int c4)
@@ -599,13 +600,16 @@ cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void*
 {
     const CUtensorMap& ta = *static_cast<const CUtensorMap*>(tmapA);
     const CUtensorMap& tb = *static_cast<const CUtensorMap*>(tmapB);
+    // (tuning switch TCONT_UMMA_IDLE_WARP=1: launch the seventh warp although nothing uses it)
+    static const bool idle_warp = std::getenv("TCONT_UMMA_IDLE_WARP") != nullptr;
+    const unsigned threads = p.producers == 2 || idle_warp ? kThreads : kThreads - 32;
     if (p.pair) {
         const long long units = ((p.tiles_m + 1) / 2) * p.tiles_n * p.k_splits;
         if (units <= 0) return cudaErrorInvalidValue;
         const long long clusters = units < num_sms / 2 ? units : num_sms / 2;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
-        cfg.blockDim = dim3(kThreads);
+        cfg.blockDim = dim3(threads);
         cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
         cfg.stream = stream;
         cudaLaunchAttribute attr[1];
@@ -620,7 +624,7 @@ cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void*
     const long long total = p.tiles_m * p.tiles_n * p.k_splits;
     if (total <= 0) return cudaErrorInvalidValue;
     const unsigned grid = static_cast<unsigned>(total < num_sms ? total : num_sms);
-    umma_tf32_kernel<false><<<grid, kThreads, smem_bytes, stream>>>(ta, tb, p);
+    umma_tf32_kernel<false><<<grid, threads, smem_bytes, stream>>>(ta, tb, p);
     return cudaGetLastError();
 }
 
