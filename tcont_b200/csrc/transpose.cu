@@ -64,6 +64,7 @@ constexpr int TILE = 64;
 struct TileGeom {
     int d0;  // merged source mode that is fastest in the destination
     int64_t tiles0, tiles1;
+    int t0, t1;  // tile extents along source mode 0 and along mode d0
 };
 
 template <>
@@ -124,17 +125,21 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const T* __restrict__
     }
 }
 
-// General case: a TILE x TILE plane over (source-fastest mode 0, destination-fastest mode d0)
-// goes through shared memory; the remaining modes are spread over the grid.
+// General case: a t0 x t1 plane over (source-fastest mode 0, destination-fastest mode d0)
+// goes through shared memory; the remaining modes are spread over the grid.  The tile extents are
+// chosen per launch so that whole tiles cover the two modes evenly (extent 72: one tile of 72, not
+// 64 + 8), up to 96 elements of 4 bytes or 64 of 8 a side.
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) permute_tiled_kernel(const T* __restrict__ src, T* __restrict__ dst, TransposeParams p,
                                                             TileGeom g)
 {
-    __shared__ T tile[TILE][TILE + 1];
+    extern __shared__ __align__(16) unsigned char tile_raw[];
+    T* tile = reinterpret_cast<T*>(tile_raw);   // [t1][t0 + 1]
+    const int pitch = g.t0 + 1;
     int64_t t = blockIdx.x;
-    const int64_t c0 = (t % g.tiles0) * TILE;  // offset along source mode 0
+    const int64_t c0 = (t % g.tiles0) * g.t0;  // offset along source mode 0
     t /= g.tiles0;
-    const int64_t r0 = (t % g.tiles1) * TILE;  // offset along source mode d0
+    const int64_t r0 = (t % g.tiles1) * g.t1;  // offset along source mode d0
     t /= g.tiles1;
     int64_t sbase = 0, dbase = 0;
     for (int i = 1; i < p.rank; ++i) {
@@ -147,36 +152,36 @@ __global__ void __launch_bounds__(256) permute_tiled_kernel(const T* __restrict_
     const int64_t e0 = p.ext[0], e1 = p.ext[g.d0];
     const int64_t s1 = p.src_stride[g.d0];  // source stride of mode d0
     const int64_t d0s = p.dst_stride[0];    // destination stride of source mode 0
-    constexpr int VPR = TILE / VEC;         // vectors per tile row
+    const int vpr0 = g.t0 / VEC, vpr1 = g.t1 / VEC;   // vectors per tile row, read side and write side
 
-    for (int idx = threadIdx.x; idx < TILE * VPR; idx += 256) {
-        const int r = idx / VPR, cv = (idx % VPR) * VEC;
+    for (int idx = threadIdx.x; idx < g.t1 * vpr0; idx += 256) {
+        const int r = idx / vpr0, cv = (idx - r * vpr0) * VEC;
         if (r0 + r < e1 && c0 + cv < e0) {
             const T* ptr = src + sbase + (r0 + r) * s1 + (c0 + cv);
             if constexpr (VEC == 1) {
-                tile[r][cv] = __ldg(ptr);
+                tile[r * pitch + cv] = __ldg(ptr);
             } else {
                 using V = typename VecOf<T>::type;
                 const V v = __ldg(reinterpret_cast<const V*>(ptr));
                 const T* e = reinterpret_cast<const T*>(&v);
 #pragma unroll
-                for (int q = 0; q < VEC; ++q) tile[r][cv + q] = e[q];
+                for (int q = 0; q < VEC; ++q) tile[r * pitch + cv + q] = e[q];
             }
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < TILE * VPR; idx += 256) {
-        const int c = idx / VPR, rv = (idx % VPR) * VEC;
+    for (int idx = threadIdx.x; idx < g.t0 * vpr1; idx += 256) {
+        const int c = idx / vpr1, rv = (idx - c * vpr1) * VEC;
         if (c0 + c < e0 && r0 + rv < e1) {
             T* ptr = dst + dbase + (c0 + c) * d0s + (r0 + rv);
             if constexpr (VEC == 1) {
-                *ptr = tile[rv][c];
+                *ptr = tile[rv * pitch + c];
             } else {
                 using V = typename VecOf<T>::type;
                 V v;
                 T* e = reinterpret_cast<T*>(&v);
 #pragma unroll
-                for (int q = 0; q < VEC; ++q) e[q] = tile[rv + q][c];
+                for (int q = 0; q < VEC; ++q) e[q] = tile[(rv + q) * pitch + c];
                 *reinterpret_cast<V*>(ptr) = v;
             }
         }
@@ -208,19 +213,30 @@ cudaError_t launch_typed(const T* src, T* dst, const TransposeParams& p, cudaStr
         else permute_rows_kernel<T, 1, int64_t><<<blocks, 256, 0, stream>>>(src, dst, p);
         return cudaGetLastError();
     }
+    bool strides_ok = true;
+    for (int i = 1; i < p.rank; ++i) strides_ok = strides_ok && p.src_stride[i] % VMAX == 0;
+    const bool vec = aligned && strides_ok && p.ext[0] % VMAX == 0 && p.ext[d0] % VMAX == 0;
+    // whole tiles of (nearly) equal size along both modes, a multiple of the vector width
+    constexpr int kTileMax = sizeof(T) == 4 ? 96 : TILE;
+    const int64_t unit = vec ? VMAX : 1;
+    // (an extent of up to kTileMax is one tile; longer ones are cut evenly into tiles of up to 64, which keep more
+    // blocks on an SM: 8192 x 8192 floats move at 5.5 TB/s with 64-wide tiles against 4.7 with 96-wide ones)
+    auto even_tile = [&](int64_t extent, int64_t* tiles) {
+        *tiles = extent <= kTileMax ? 1 : (extent + TILE - 1) / TILE;
+        const int64_t per = (extent + *tiles - 1) / *tiles;
+        return static_cast<int>((per + unit - 1) / unit * unit);
+    };
     TileGeom g;
     g.d0 = d0;
-    g.tiles0 = (p.ext[0] + TILE - 1) / TILE;
-    g.tiles1 = (p.ext[d0] + TILE - 1) / TILE;
+    g.t0 = even_tile(p.ext[0], &g.tiles0);
+    g.t1 = even_tile(p.ext[d0], &g.tiles1);
     int64_t blocks = g.tiles0 * g.tiles1;
     for (int i = 1; i < p.rank; ++i)
         if (i != d0) blocks *= p.ext[i];
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
-    bool strides_ok = true;
-    for (int i = 1; i < p.rank; ++i) strides_ok = strides_ok && p.src_stride[i] % VMAX == 0;
-    const bool vec = aligned && strides_ok && p.ext[0] % VMAX == 0 && p.ext[d0] % VMAX == 0;
-    if (vec) permute_tiled_kernel<T, VMAX><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, dst, p, g);
-    else permute_tiled_kernel<T, 1><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, dst, p, g);
+    const size_t smem = static_cast<size_t>(g.t1) * static_cast<size_t>(g.t0 + 1) * sizeof(T);   // at most 37 KB
+    if (vec) permute_tiled_kernel<T, VMAX><<<static_cast<unsigned>(blocks), 256, smem, stream>>>(src, dst, p, g);
+    else permute_tiled_kernel<T, 1><<<static_cast<unsigned>(blocks), 256, smem, stream>>>(src, dst, p, g);
     return cudaGetLastError();
 }
 

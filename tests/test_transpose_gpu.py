@@ -38,6 +38,9 @@ def test_all_permutations_rank4(engine, dtype):
     ([48, 8, 48], [0, 2, 1]),               # cfg4's B[c,f,d] -> [c,d,f]
     ([130, 70], [1, 0]), ([67, 3, 129], [2, 1, 0]), ([1, 7, 1, 9], [3, 0, 1, 2]),
     ([256, 1024, 16], [1, 0, 2]), ([33, 2, 3, 4, 5], [4, 2, 0, 3, 1]),
+    # tile extents chosen per launch: one tile of 72, of 96; two of 52 / 50 (4-byte) or 56 / 52 (8-byte); 97 and 200
+    ([72, 5, 3, 72], [3, 1, 2, 0]), ([96, 3, 96], [2, 1, 0]), ([100, 104], [1, 0]), ([97, 2, 200], [2, 1, 0]),
+    ([8, 300], [1, 0]), ([300, 8], [1, 0]),
 ])
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_selected_shapes(engine, extent, perm, dtype):
