@@ -497,7 +497,11 @@ void plan_umma_impl(const Problem& p_in, const CostTable& cost, UmmaSpec* u, int
     // (A K-major FP64 operand then has 64-byte rows under the 64-byte swizzle; the tcgen05 kernel keeps
     // 128-byte rows for K-major operands.)
     if (f64) BK = kc_ext <= 8 || double(ceil_div(kc_ext, 16) * 16) > 1.15 * double(ceil_div(kc_ext, 8) * 8) ? 8 : 16;
-    else if (!a_kmajor && !b_kmajor) BK = kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32;
+    else if (!a_kmajor && !b_kmajor) {
+        BK = kc_ext <= 8 ? 8 : kc_ext <= 16 ? 16 : 32;
+        // chunks of 24 (three MMAs per stage) where 32 would pad the mode by over 15 % and 24 by nothing: extents 24, 72, 120
+        if (kc_ext % 24 == 0 && double(ceil_div(kc_ext, 32) * 32) > 1.15 * double(kc_ext) && !std::getenv("TCONT_UMMA_NO_BK24")) BK = 24;
+    }
     // A k chunk of 64 (eight MMAs per stage, stages of 64 KB per CTA of a pair): half the barrier round trips and
     // half the copy instructions per flop.  The producer warp needs 700 to 900 cycles per stage for its
     // wait / announce / copy sequence whatever the stage holds, which is more than the 512 cycles four MMAs take

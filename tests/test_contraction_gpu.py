@@ -91,6 +91,8 @@ UMMA_SHAPES = {
     "case31_like": Contraction("abcdef", "dega", "gfbc", dict(a=8, b=4, c=4, d=24, e=4, f=8, g=24), F32),
     "long_k": Contraction("ab", "acd", "dbc", dict(a=312, b=296, c=40, d=36), F32),             # 30 tiles, 45 k iterations: split-K
     "long_k_ragged": Contraction("ab", "ak", "kb", dict(a=200, b=120, k=1000), F32),            # last k range shorter than the others
+    "k_chunks_of_24": Contraction("abcd", "aebf", "cfde", dict(a=128, b=3, c=64, d=5, e=5, f=72), F32),   # both MN-major, chunked mode 72 = 3 x 24
+    "k_chunk_24_once": Contraction("abcd", "aebf", "cfde", dict(a=96, b=4, c=40, d=6, e=7, f=24), F32),   # one chunk of 24 per other-k index
 }
 
 
@@ -108,6 +110,8 @@ def test_tensor_core_shapes(engine, oracle, monkeypatch, name, splitk):
         assert desc["umma"]["k_splits"] == 1
     if splitk == "auto" and name == "long_k":   # (long_k_ragged is too small for a second kernel to pay)
         assert desc["umma"]["k_splits"] > 1
+    if name.startswith("k_chunk"):
+        assert desc["umma"]["BK"] == 24, desc["umma"]
     check(oracle, c, A, B, out, desc)
 
 
