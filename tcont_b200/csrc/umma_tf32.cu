@@ -147,7 +147,10 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 //               the issuing CTA), CTA 0 issues the MMAs for both, each CTA drains its own 128 x BN
 //               accumulator.  B traffic per flop halves, which is what the operand-fetch-bound 1-CTA
 //               kernel lacks.
-template <bool PAIR>
+// NP = producer warps (1, or 2 taking turns stage by stage); a template parameter so that the one-producer loop,
+// whose pass per stage is the tightest thing in the pair kernel, carries none of the two-producer bookkeeping
+// (with it as a run-time value the pair kernel lost 8 %).
+template <bool PAIR, int NP>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                  const __grid_constant__ UmmaParams p)
@@ -210,12 +213,13 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
     const uint32_t first_unit = PAIR ? blockIdx.x / 2u : blockIdx.x;
     const uint32_t unit_step = PAIR ? gridDim.x / 2u : gridDim.x;
 
-    if (warp == 0 || (warp == 6 && p.producers == 2)) {
+    if (warp == 0 || (warp == 6 && NP == 2)) {
         // ---------------- TMA producer: lane i owns slab i of the stage ----------------
         // With two producers (p.producers == 2, an even number of stages) warp 0 fills the even k iterations of the
         // CTA and warp 6 the odd ones: the wait-announce-copy round trip of one warp may then take two stages' worth
         // of MMA time, which is what lets stages be half as large and the ring twice as deep.
-        const int np = p.producers == 2 ? 2 : 1, pi = warp == 0 ? 0 : 1;
+        constexpr int np = NP;
+        const int pi = warp == 0 ? 0 : 1;
         // lane i owns copy i of the stage; a copy brings slabs_per_op consecutive slabs
         const int OA = SA / p.a.slabs_per_op, OBL = SBL / p.b.slabs_per_op;
         const bool is_a = lane < OA;
@@ -590,9 +594,13 @@ umma_tf32_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constan
 // the same opt-in maximum, so runs with different stage counts can live side by side.
 cudaError_t umma_tf32_configure()
 {
-    cudaError_t e = cudaFuncSetAttribute(umma_tf32_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(umma_tf32_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmemBytes);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(umma_tf32_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmemBytes);
+    e = cudaFuncSetAttribute(umma_tf32_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(umma_tf32_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(umma_tf32_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmemBytes);
 }
 
 cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void* tmapB, int smem_bytes, int num_sms,
@@ -619,12 +627,14 @@ cudaError_t launch_umma_tf32(const UmmaParams& p, const void* tmapA, const void*
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        return cudaLaunchKernelEx(&cfg, umma_tf32_kernel<true>, ta, tb, p);
+        if (p.producers == 2) return cudaLaunchKernelEx(&cfg, umma_tf32_kernel<true, 2>, ta, tb, p);
+        return cudaLaunchKernelEx(&cfg, umma_tf32_kernel<true, 1>, ta, tb, p);
     }
     const long long total = p.tiles_m * p.tiles_n * p.k_splits;
     if (total <= 0) return cudaErrorInvalidValue;
     const unsigned grid = static_cast<unsigned>(total < num_sms ? total : num_sms);
-    umma_tf32_kernel<false><<<grid, threads, smem_bytes, stream>>>(ta, tb, p);
+    if (p.producers == 2) umma_tf32_kernel<false, 2><<<grid, threads, smem_bytes, stream>>>(ta, tb, p);
+    else umma_tf32_kernel<false, 1><<<grid, threads, smem_bytes, stream>>>(ta, tb, p);
     return cudaGetLastError();
 }
 
