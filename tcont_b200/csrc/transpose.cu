@@ -129,17 +129,19 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const T* __restrict__
 // goes through shared memory; the remaining modes are spread over the grid.  The tile extents are
 // chosen per launch so that whole tiles cover the two modes evenly (extent 72: one tile of 72, not
 // 64 + 8), up to 96 elements of 4 bytes or 64 of 8 a side.
-template <typename T, int VEC>
-__global__ void __launch_bounds__(256) permute_tiled_kernel(const T* __restrict__ src, T* __restrict__ dst, TransposeParams p,
+// FIXED: 64 x 64 tiles known at compile time (the loops unroll; 4 to 7 % faster where such tiles fit the extents well).
+template <typename T, int VEC, bool FIXED>
+__global__ void __launch_bounds__(256, sizeof(T) == 4 ? 8 : 6) permute_tiled_kernel(const T* __restrict__ src, T* __restrict__ dst, TransposeParams p,
                                                             TileGeom g)
 {
     extern __shared__ __align__(16) unsigned char tile_raw[];
     T* tile = reinterpret_cast<T*>(tile_raw);   // [t1][t0 + 1]
-    const int pitch = g.t0 + 1;
+    const int t0 = FIXED ? TILE : g.t0, t1 = FIXED ? TILE : g.t1;
+    const int pitch = t0 + 1;
     int64_t t = blockIdx.x;
-    const int64_t c0 = (t % g.tiles0) * g.t0;  // offset along source mode 0
+    const int64_t c0 = (t % g.tiles0) * t0;  // offset along source mode 0
     t /= g.tiles0;
-    const int64_t r0 = (t % g.tiles1) * g.t1;  // offset along source mode d0
+    const int64_t r0 = (t % g.tiles1) * t1;  // offset along source mode d0
     t /= g.tiles1;
     int64_t sbase = 0, dbase = 0;
     for (int i = 1; i < p.rank; ++i) {
@@ -152,37 +154,61 @@ __global__ void __launch_bounds__(256) permute_tiled_kernel(const T* __restrict_
     const int64_t e0 = p.ext[0], e1 = p.ext[g.d0];
     const int64_t s1 = p.src_stride[g.d0];  // source stride of mode d0
     const int64_t d0s = p.dst_stride[0];    // destination stride of source mode 0
-    const int vpr0 = g.t0 / VEC, vpr1 = g.t1 / VEC;   // vectors per tile row, read side and write side
+    const int vpr0 = t0 / VEC, vpr1 = t1 / VEC;   // vectors per tile row, read side and write side
 
-    for (int idx = threadIdx.x; idx < g.t1 * vpr0; idx += 256) {
-        const int r = idx / vpr0, cv = (idx - r * vpr0) * VEC;
-        if (r0 + r < e1 && c0 + cv < e0) {
-            const T* ptr = src + sbase + (r0 + r) * s1 + (c0 + cv);
-            if constexpr (VEC == 1) {
-                tile[r * pitch + cv] = __ldg(ptr);
-            } else {
-                using V = typename VecOf<T>::type;
-                const V v = __ldg(reinterpret_cast<const V*>(ptr));
-                const T* e = reinterpret_cast<const T*>(&v);
+    // Slots (one vector each) are handled two at a time per thread, both global loads issued before either is used;
+    // the kernel is held to 32 registers so that eight blocks share an SM (with 48 it lost a fifth of its rate).
+    // slot / vpr by multiplication: exact for slot < 2^20 / vpr (at most 96 x 96 slots, vpr at most 96).
+    const unsigned inv0 = (1u << 20) / static_cast<unsigned>(vpr0) + 1u, inv1 = (1u << 20) / static_cast<unsigned>(vpr1) + 1u;
+    const int slots0 = t1 * vpr0, slots1 = t0 * vpr1;
+    using V = typename VecOf<T>::type;
+    for (int base = threadIdx.x; base < slots0; base += 2 * 256) {
+        int at[2];
+        bool ok[2];
+        V val[2];
+        T one[2];
 #pragma unroll
-                for (int q = 0; q < VEC; ++q) tile[r * pitch + cv + q] = e[q];
+        for (int u = 0; u < 2; ++u) {
+            const int idx = base + u * 256;
+            const int r = static_cast<int>((static_cast<unsigned>(idx) * inv0) >> 20), cv = (idx - r * vpr0) * VEC;
+            ok[u] = idx < slots0 && r0 + r < e1 && c0 + cv < e0;
+            at[u] = r * pitch + cv;
+            if (ok[u]) {
+                const T* ptr = src + sbase + (r0 + r) * s1 + (c0 + cv);
+                if constexpr (VEC == 1) one[u] = __ldg(ptr);
+                else val[u] = __ldg(reinterpret_cast<const V*>(ptr));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (ok[u]) {
+                if constexpr (VEC == 1) {
+                    tile[at[u]] = one[u];
+                } else {
+                    const T* e = reinterpret_cast<const T*>(&val[u]);
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) tile[at[u] + q] = e[q];
+                }
             }
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < g.t0 * vpr1; idx += 256) {
-        const int c = idx / vpr1, rv = (idx - c * vpr1) * VEC;
-        if (c0 + c < e0 && r0 + rv < e1) {
-            T* ptr = dst + dbase + (c0 + c) * d0s + (r0 + rv);
-            if constexpr (VEC == 1) {
-                *ptr = tile[rv * pitch + c];
-            } else {
-                using V = typename VecOf<T>::type;
-                V v;
-                T* e = reinterpret_cast<T*>(&v);
+    for (int base = threadIdx.x; base < slots1; base += 2 * 256) {
 #pragma unroll
-                for (int q = 0; q < VEC; ++q) e[q] = tile[(rv + q) * pitch + c];
-                *reinterpret_cast<V*>(ptr) = v;
+        for (int u = 0; u < 2; ++u) {
+            const int idx = base + u * 256;
+            const int c = static_cast<int>((static_cast<unsigned>(idx) * inv1) >> 20), rv = (idx - c * vpr1) * VEC;
+            if (idx < slots1 && c0 + c < e0 && r0 + rv < e1) {
+                T* ptr = dst + dbase + (c0 + c) * d0s + (r0 + rv);
+                if constexpr (VEC == 1) {
+                    *ptr = tile[rv * pitch + c];
+                } else {
+                    V out;
+                    T* e = reinterpret_cast<T*>(&out);
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) e[q] = tile[(rv + q) * pitch + c];
+                    *reinterpret_cast<V*>(ptr) = out;
+                }
             }
         }
     }
@@ -230,13 +256,23 @@ cudaError_t launch_typed(const T* src, T* dst, const TransposeParams& p, cudaStr
     g.d0 = d0;
     g.t0 = even_tile(p.ext[0], &g.tiles0);
     g.t1 = even_tile(p.ext[d0], &g.tiles1);
+    // fixed 64 x 64 tiles where they waste less than 45 % of their slots on these extents
+    auto eff64 = [](int64_t e) { return double(e) / double((e + TILE - 1) / TILE * TILE); };
+    const bool fixed = eff64(p.ext[0]) * eff64(p.ext[d0]) >= 0.55;
+    if (fixed) {
+        g.t0 = g.t1 = TILE;
+        g.tiles0 = (p.ext[0] + TILE - 1) / TILE;
+        g.tiles1 = (p.ext[d0] + TILE - 1) / TILE;
+    }
     int64_t blocks = g.tiles0 * g.tiles1;
     for (int i = 1; i < p.rank; ++i)
         if (i != d0) blocks *= p.ext[i];
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
     const size_t smem = static_cast<size_t>(g.t1) * static_cast<size_t>(g.t0 + 1) * sizeof(T);   // at most 37 KB
-    if (vec) permute_tiled_kernel<T, VMAX><<<static_cast<unsigned>(blocks), 256, smem, stream>>>(src, dst, p, g);
-    else permute_tiled_kernel<T, 1><<<static_cast<unsigned>(blocks), 256, smem, stream>>>(src, dst, p, g);
+    if (vec && fixed) permute_tiled_kernel<T, VMAX, true><<<static_cast<unsigned>(blocks), 256, smem, stream>>>(src, dst, p, g);
+    else if (vec) permute_tiled_kernel<T, VMAX, false><<<static_cast<unsigned>(blocks), 256, smem, stream>>>(src, dst, p, g);
+    else if (fixed) permute_tiled_kernel<T, 1, true><<<static_cast<unsigned>(blocks), 256, smem, stream>>>(src, dst, p, g);
+    else permute_tiled_kernel<T, 1, false><<<static_cast<unsigned>(blocks), 256, smem, stream>>>(src, dst, p, g);
     return cudaGetLastError();
 }
 
