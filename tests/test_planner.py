@@ -237,3 +237,24 @@ def test_sub_tensor_views_take_their_strides_from_the_parent(engine):
     assert engine.plan_views(to_equation(engine, lk, 1), [320, 296], None, None).describe()["umma"]["k_splits"] == 1
     with pytest.raises(ValueError):
         engine.plan_views(eq, None, [40, 48, 24, 24], None)   # parent smaller than the view
+
+
+def test_tcgen05_kernel_forms(engine, monkeypatch):
+    """Which form of the tcgen05 kernel a plan asks for: CTA pairs with stages of 64 k and one producer warp for
+    large problems; one CTA per tile with two producer warps (and an even number of stages) otherwise; k chunks of
+    24 where 32 would pad an MN-major contracted mode by a quarter."""
+    from oracle_lib import F32
+    pair = describe(engine, CONFIGS["cfg2"][0])["umma"]
+    assert pair["pair"] is True and pair["BK"] == 64 and pair["producers"] == 1 and pair["stages"] == 3
+    # the 72-extent 4-D family (reference case 22): both operands MN-major, chunked mode of extent 72
+    c22 = Contraction("abcd", "aecf", "bfde", dict(a=72, b=72, c=72, d=72, e=72, f=72), F32)
+    one = describe(engine, c22, 1)["umma"]
+    assert one["pair"] is False and one["producers"] == 2 and one["stages"] % 2 == 0 and one["BK"] == 24
+    monkeypatch.setenv("TCONT_UMMA_NO_BK24", "1")
+    assert describe(engine, c22, 1)["umma"]["BK"] == 32
+    monkeypatch.delenv("TCONT_UMMA_NO_BK24")
+    # one k iteration per tile (the low-K configuration after its transposes): a second producer has nothing to do
+    low_k = describe(engine, CONFIGS["cfg4"][0])["umma"]
+    assert low_k["pair"] is False and low_k["producers"] == 1
+    monkeypatch.setenv("TCONT_UMMA_PRODUCERS", "1")
+    assert describe(engine, c22, 1)["umma"]["producers"] == 1
