@@ -71,10 +71,6 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster)
-{
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
-}
 // One commit that arrives on the barrier at the same offset in both CTAs of the pair.
 __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar)
 {
