@@ -119,22 +119,22 @@ struct CostTable {
     // Defaults: what `python -m tcont_b200.calibrate` measured on a B200 (the file it writes,
     // tcont_cost_table.NVIDIA_B200.txt beside the library, holds the same figures and is read when the current
     // device has that name; TCONT_COST_TABLE names another "key value" file).
-    double hbm_gbs = 6186.1;                // copy through the permutation kernel, read + write
-    double umma_tf32_tflops = 682.8;        // tcgen05 kernel, 8192 x 8192 x 4096, CTA pairs with a k chunk of 64
+    double hbm_gbs = 6178.9;                // copy through the permutation kernel, read + write
+    double umma_tf32_tflops = 674.4;        // tcgen05 kernel, 8192 x 8192 x 4096, CTA pairs with a k chunk of 64
     double simt_f32_tflops = 23.7;
     double simt_f64_tflops = 16.4;
-    double dmma_f64_tflops = 33.7;          // TMA-fed tensor-path kernel
+    double dmma_f64_tflops = 33.5;          // TMA-fed tensor-path kernel
     double dmma_f64_gather_tflops = 20.8;   // gather tensor-path kernel, 16-byte gathers
     double dmma_f64_gather8_tflops = 15.5;  // gather tensor-path kernel, an operand on 8-byte gathers
     double dmma_f64_gather_narrow_tflops = 6.5;  // gather tensor-path kernel, 256 x 32 tiles (N <= 48)
-    double scatter_store_ps = 28.0;         // per element of C stored on its own (TMA-fed FP64 kernel)
-    double scatter_store_f32_ps = 18.6;     // the same for the tcgen05 kernel's 4-byte elements
-    double launch_us = 7.9;                 // one more launch through the library (a contraction too small to matter, in a loop)
+    double scatter_store_ps = 27.6;         // per element of C stored on its own (TMA-fed FP64 kernel)
+    double scatter_store_f32_ps = 17.6;     // the same for the tcgen05 kernel's 4-byte elements
+    double launch_us = 6.9;                 // one more launch through the library (a contraction too small to matter, in a loop)
     // Fraction of the tcgen05 rate lost per unit of staged bytes whose K rows lie 2 MB or more apart, i.e. every row
     // of a TMA box in another 2 MB page (the calibration probe: the large 4-D configuration with f = 64, A's rows 8 MB
     // apart, half of a pair's bytes; the configuration itself: 18.7 ms where A lies against 14.1 ms through the
     // transpose that brings the rows together, i.e. 0.53; with rows 1 MB apart there is no loss: 701 / 689 TFLOP/s).
-    double far_row_penalty = 0.43;
+    double far_row_penalty = 0.47;
     // Least time per stage of the tcgen05 kernel's ring, whatever the stage holds: one pass of the producer's
     // wait-announce-copy sequence (700 to 900 cycles in the main-loop probes).
     double umma_stage_us = 0.45;
