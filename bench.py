@@ -83,7 +83,8 @@ REASON_BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdo
 def summarise_clock_samples(samples, windows):
     """samples: (time, gpu index, sm MHz, max sm MHz, power W, reasons bit mask) tuples read from NVML while the
     benchmark runs; windows: {name: (t0, t1)} host-clock brackets of the timed regions.  Returns the `clocks`
-    object: the median SM clock under load (upper half of what was seen), the throttle reasons seen at all and
+    object: the median SM clock under load (inside the headline timed region; the upper half of everything seen if that
+    region holds no sample), the throttle reasons seen at all and
     those seen inside the headline timed region, and per window its sample count, median clock and reasons."""
     def reasons_of(rows):
         out = set()
@@ -106,6 +107,10 @@ def summarise_clock_samples(samples, windows):
         per[name] = {"samples": len(rows), "sm_mhz": statistics.median(r[2] for r in rows) if rows else None,
                      "reasons": reasons_of(rows), "seconds": t1 - t0}
     head = per.get("headline", {"samples": 0, "reasons": [], "sm_mhz": None})
+    # "under load" is the headline timed region where it holds samples: an idle GPU (during the CPU legs of the run)
+    # shows the maximum clock, a power-capped one under load a lower one
+    if head["samples"]:
+        out["sm_mhz"] = head["sm_mhz"]
     out["samples_in_timed_region"] = head["samples"]
     out["reasons_in_timed_region"] = head["reasons"]
     out["sm_mhz_in_timed_region"] = head["sm_mhz"]

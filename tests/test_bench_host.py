@@ -24,6 +24,9 @@ def test_clock_samples_are_attributed_to_the_timed_regions():
     assert c["samples"] == 6 and c["samples_in_timed_region"] == 3
     assert c["reasons"] == ["sw_power_cap", "sw_thermal_slowdown"] and c["reasons_in_timed_region"] == []
     assert c["sm_max_mhz"] == 1965.0 and c["sm_mhz_in_timed_region"] == 1950.0
+    assert c["sm_mhz"] == 1950.0      # "under load" = the headline timed region, not the idle samples around it
+    no_window = bench.summarise_clock_samples(samples, {"headline": (t0 + 9.0, t0 + 9.5)})
+    assert no_window["samples_in_timed_region"] == 0 and no_window["sm_mhz"] is not None   # falls back to what was seen
     assert c["windows"]["cfg2"]["samples"] == 1 and c["windows"]["cfg2"]["reasons"] == ["sw_thermal_slowdown"]
     assert c["power_w_max"] == 995.0
     empty = bench.summarise_clock_samples([], {"headline": (t0, t0 + 1)})
